@@ -221,7 +221,10 @@ extern "C" int moeb_route_plan_rows(int T, int k, int E, int pad) {
 
 extern "C" size_t moeb_route_plan_workspace_bytes(int T, int k, int E) {
   if (T < 0 || k <= 0 || E <= 0) return 0;
-  const size_t n_chunks = ((size_t)T * k + moeb::kPlanChunk - 1) / moeb::kPlanChunk;
+  size_t n_chunks = ((size_t)T * k + moeb::kPlanChunk - 1) / moeb::kPlanChunk;
+  // With T == 0 one CTA still runs (it clears the row maps) and stores one
+  // histogram row of E words, so the table never has fewer than one row.
+  if (n_chunks == 0) n_chunks = 1;
   // chunk bases + one int32 counter of out-of-range indices, rounded to 256 B
   return ((n_chunks * E + 1) * sizeof(int32_t) + 255) / 256 * 256;
 }
@@ -238,8 +241,12 @@ extern "C" int moeb_route_plan(const int32_t* indices, int T, int k, int E, int 
     set_last_error_msg("moeb_route_plan: bad argument (need 0 < E <= 1024, k > 0, pad > 0)");
     return kInvalidArgument;
   }
-  if (m_cap < moeb_route_plan_rows(T, k, E, pad) ||
-      workspace_bytes < moeb_route_plan_workspace_bytes(T, k, E)) {
+  const int rows_needed = moeb_route_plan_rows(T, k, E, pad);
+  if (rows_needed < 0 || (long long)T * k > 0x7fffffffLL) {
+    set_last_error_msg("moeb_route_plan: T * k (plus padding) does not fit in 32 bits");
+    return kTooLarge;
+  }
+  if (m_cap < rows_needed || workspace_bytes < moeb_route_plan_workspace_bytes(T, k, E)) {
     set_last_error_msg("moeb_route_plan: m_cap or workspace too small");
     return kInvalidArgument;
   }
@@ -247,7 +254,8 @@ extern "C" int moeb_route_plan(const int32_t* indices, int T, int k, int E, int 
   const int n_pairs = T * k;
   const int n_chunks = ceil_div(n_pairs, kPlanChunk);
   int32_t* chunk_counts = (int32_t*)workspace;
-  int32_t* bad_index = chunk_counts + (size_t)n_chunks * E;
+  // behind the table, which has at least one row (the CTA that runs for T == 0)
+  int32_t* bad_index = chunk_counts + (size_t)(n_chunks > 0 ? n_chunks : 1) * E;
   MOEB_CUDA_TRY(cudaMemsetAsync(bad_index, 0, sizeof(int32_t), s));
   // at least one CTA so that the row maps are cleared even when T == 0
   const int grid = n_chunks > 0 ? n_chunks : 1;
@@ -336,9 +344,10 @@ extern "C" int moeb_route_plan_static(const int32_t* indices, int T, int k, int 
     set_last_error_msg("moeb_route_plan_static: bad argument (need 0 < E <= 1024, k > 0, pad > 0)");
     return kInvalidArgument;
   }
-  if (m_cap < moeb_route_plan_rows(T, k, E, pad)) {
-    set_last_error_msg("moeb_route_plan_static: m_cap too small");
-    return kInvalidArgument;
+  const int rows_needed = moeb_route_plan_rows(T, k, E, pad);
+  if (rows_needed < 0 || m_cap < rows_needed) {
+    set_last_error_msg("moeb_route_plan_static: m_cap too small (or T * k beyond 32 bits)");
+    return rows_needed < 0 ? kTooLarge : kInvalidArgument;
   }
   const long long n_pairs_ll = (long long)T * k;
   const long long n_chunks_ll = (n_pairs_ll + kPlanChunk - 1) / kPlanChunk;

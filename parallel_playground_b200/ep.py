@@ -439,6 +439,7 @@ class All2AllP2P:
         self.grouped_layout = torch.empty(self.m_cap, **i32)
         self.source_rank = torch.empty(self.m_cap, **i32)
         self._dummy = torch.empty(1, **i32)
+        self._minus_one = torch.full((1, 1), -1, **i32)
         self._n_tokens = 0
         # nobody touches a peer buffer (the flags included) before every rank has
         # mapped and zeroed them: one NCCL barrier at set-up, none afterwards
@@ -526,7 +527,10 @@ class All2AllP2P:
         (moeb_fp8_grouped_gemm_nt_scatter); reduce them locally."""
         self.fence()                                        # every rank's rows have come home
         T = self._n_tokens
-        self._mc.unpermute_combine(self.home, self.home_rows[:T], weights, out_tokens, accumulate)
+        # copies the dispatch dropped (capacity overflow, expert id out of range)
+        # never came home: their home rows hold stale data and stay out of the sum
+        rows = torch.where(self.dst_row[:T] >= 0, self.home_rows[:T], self._minus_one)
+        self._mc.unpermute_combine(self.home, rows, weights, out_tokens, accumulate)
 
     def combine(self, out_tokens, weights, accumulate=False):
         """Pull this rank's tokens' expert outputs from `expert_y` of their owners

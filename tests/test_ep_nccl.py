@@ -141,6 +141,17 @@ def _worker(rank, world, port, q):
         total = torch.tensor([int(small.overflow.item())], device=dev)
         dist.all_reduce(total)
         assert int(total.item()) > 0
+        # dropped copies stay out of the sum in both combine forms: push == pull bits
+        # (the home buffer is poisoned first, so a stale row would show)
+        small.home.fill_(1000.0)
+        out7, out8 = torch.full_like(out, 1.0), torch.full_like(out, 2.0)
+        ep_moe_forward_p2p(small, d.x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale,
+                           d.down, d.down_scale, out7, shape, {})
+        ep_moe_forward_p2p(small, d.x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale,
+                           d.down, d.down_scale, out8, shape, {}, push_combine=False)
+        torch.cuda.synchronize()
+        assert torch.equal(out7.view(torch.int16), out8.view(torch.int16))
+        assert float(out7.float().abs().max()) < 100.0
         dist.barrier()
         dist.destroy_process_group()
         q.put((rank, "ok"))

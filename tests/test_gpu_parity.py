@@ -86,6 +86,7 @@ def _random_indices(T, E, k, seed, skew=False):
 @pytest.mark.parametrize("T,E,k,skew", [
     (1, 4, 1, False), (256, 8, 2, False), (8192, 32, 8, True), (4096, 256, 8, False),
     (1000, 64, 10, True), (300, 1024, 12, False), (0, 8, 2, False), (16384, 8, 2, True),
+    (0, 256, 8, False), (0, 1024, 8, False),
 ])
 def test_route_plan_bit_exact(mc, oracle_mod, T, E, k, skew):
     idx = _random_indices(T, E, k, seed=T + E + k, skew=skew)
@@ -99,6 +100,32 @@ def test_route_plan_bit_exact(mc, oracle_mod, T, E, k, skew):
     assert np.array_equal(plan.src_token.cpu().numpy(), ref.src_token)
     assert np.array_equal(plan.src_slot.cpu().numpy(), ref.src_slot)
     assert np.array_equal(plan.grouped_layout.cpu().numpy(), ref.grouped_layout)
+
+
+@pytest.mark.parametrize("E", [256, 1024])
+def test_route_plan_no_tokens_stays_inside_its_workspace(lib, E):
+    """A rank that brings no tokens (T == 0): the one CTA that still runs must
+    not write past the workspace the size query asks for. The workspace sits in
+    the middle of a poisoned buffer; the guard words on both sides must survive."""
+    from parallel_playground_b200 import cabi
+    T, k = 0, 8
+    ws_bytes = lib.moeb_route_plan_workspace_bytes(T, k, E)
+    assert ws_bytes >= (E + 1) * 4
+    guard = 8192
+    raw = torch.full((guard + ws_bytes + guard,), 0x5A, dtype=torch.uint8, device=DEV)
+    ws = raw[guard:guard + ws_bytes]
+    m_cap = lib.moeb_route_plan_rows(T, k, E, 128)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    counts = torch.full((E,), -7, **i32)
+    poff = torch.full((E + 1,), -7, **i32)
+    maps = [torch.full((m_cap,), -7, **i32) for _ in range(3)]
+    cabi.call("moeb_route_plan", None, T, k, E, 128, m_cap, counts.data_ptr(), poff.data_ptr(),
+              None, maps[0].data_ptr(), maps[1].data_ptr(), maps[2].data_ptr(), ws.data_ptr(),
+              ws_bytes, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert bool((raw[:guard] == 0x5A).all()) and bool((raw[guard + ws_bytes:] == 0x5A).all())
+    assert int(counts.abs().sum()) == 0 and int(poff.abs().sum()) == 0
+    assert all(bool((m == -1).all()) for m in maps)
 
 
 def test_route_plan_all_tokens_one_expert(mc, oracle_mod):
@@ -737,6 +764,73 @@ def test_full_size_gemm_linearity_and_sampled_rows(mc, oracle_mod):
                                             q(inp.down[e:e + 1]),
                                             inp.down_scale[e:e + 1].cpu().numpy(), sub_layout)
         assert oracle_mod.calc_diff(y_ref, y[rows].cpu()) < 1e-5
+
+
+@pytest.mark.parametrize("name,T,E_local,k", [
+    ("dsv3_prefill", 4096, 32, 8),     # H=7168, I=2048: one rank's 32 experts at EP=8
+    ("mixtral", 32768, 1, 1),          # H=4096, I=14336: one expert per rank at EP=8
+    ("qwen3", 8192, 128, 8),           # H=2048, I=768: all 128 experts on one GPU
+])
+def test_full_shape_sampled_row_blocks(mc, oracle_mod, name, T, E_local, k):
+    """The model-shaped configurations at their full H and I (and a full rank's
+    worth of rows): three experts x one 128-row block each go through the CPU
+    oracle, gate/up + SwiGLU + re-quantisation and the down projection
+    (same-FP8-input bars: calc_diff < 1e-3 and < 1e-5)."""
+    import dataclasses
+    from parallel_playground_b200 import workloads as wl
+    base = wl.CONFIGS[name]
+    shape = dataclasses.replace(base, E=E_local, T=T, k=k, zipf_bias=0.0)
+    H, I = shape.H, shape.I
+    inp = wl.make_layer_inputs(shape, weights_device=DEV)
+    g = torch.Generator().manual_seed(11)
+    idx = torch.rand(T, E_local, generator=g).argsort(1)[:, :k].int().contiguous()
+    plan = mc.route_plan(idx.to(DEV), E_local)
+    M = plan.m_cap
+    ex = torch.zeros((M, H), dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    es = torch.ones((H // 128, M), dtype=torch.float32, device=DEV)
+    mc.permute_quant(inp.x.to(DEV), plan.dst_row, ex, es)
+    D = torch.zeros((M, I), dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    sd = torch.zeros((I // 128, M), dtype=torch.float32, device=DEV)
+    mc.fp8_grouped_gemm_swiglu(ex, es, inp.gate, inp.gate_scale, inp.up, inp.up_scale, D, sd,
+                               mc.GemmType.MGroupedContiguous, plan.grouped_layout)
+    y = torch.empty((M, H), dtype=torch.bfloat16, device=DEV)
+    mc.fp8_grouped_gemm_nt(D, sd, inp.down, inp.down_scale, y, mc.GemmType.MGroupedContiguous,
+                           plan.grouped_layout)
+    mc.check_device_status()
+    layout = plan.grouped_layout.cpu().numpy()
+    offs = plan.padded_offsets.cpu().numpy()
+    q = lambda t: t.view(torch.uint8).cpu().numpy()  # noqa: E731
+    checked = 0
+    for e in sorted({0, E_local // 2, E_local - 1}):
+        # a block from the middle of the expert's range (its last block holds the padding)
+        n_blocks = (int(offs[e + 1]) - int(offs[e])) // 128
+        for r0 in {int(offs[e]), int(offs[e]) + 128 * (n_blocks - 1)}:
+            rows = np.arange(r0, r0 + 128)
+            rows = rows[layout[rows] >= 0]
+            if rows.size == 0:
+                continue
+            sub_layout = np.zeros(rows.size, np.int32)
+            a_q = q(ex[rows[0]:rows[-1] + 1])
+            a_s = np.ascontiguousarray(es[:, rows[0]:rows[-1] + 1].cpu().numpy())
+            _, d_ref, sd_ref = oracle_mod.grouped_gemm_swiglu_ref(
+                a_q, a_s, q(inp.gate[e:e + 1]), inp.gate_scale[e:e + 1].cpu().numpy(),
+                q(inp.up[e:e + 1]), inp.up_scale[e:e + 1].cpu().numpy(), sub_layout)
+            d_gpu = q(D[rows[0]:rows[-1] + 1])
+            sd_gpu = np.ascontiguousarray(sd[:, rows[0]:rows[-1] + 1].cpu().numpy())
+            out = oracle_mod.dequant_rows(d_gpu, sd_gpu)
+            ref = oracle_mod.dequant_rows(d_ref, sd_ref)
+            assert oracle_mod.calc_diff(ref, out) < 1e-3, (name, e, r0)
+            y_ref = oracle_mod.grouped_gemm_ref(d_gpu, sd_gpu, q(inp.down[e:e + 1]),
+                                                inp.down_scale[e:e + 1].cpu().numpy(), sub_layout)
+            assert oracle_mod.calc_diff(y_ref, y[rows[0]:rows[-1] + 1].float().cpu()) < 1e-5, \
+                (name, e, r0)
+            checked += 1
+    assert checked >= 2
+    # padding rows of the intermediate are zeros with scale 1 (never NaN)
+    pad_rows = torch.from_numpy(np.nonzero(layout[:int(offs[-1])] < 0)[0]).to(DEV)
+    if pad_rows.numel():
+        assert int(D.view(torch.uint8)[pad_rows].max()) == 0
+        assert not bool(torch.isnan(y[pad_rows].float()).any())
 
 
 # ------------------------------------------------ compiled C++ binding ------

@@ -40,6 +40,8 @@ def _run(lib, name, idx_dev, T, k, E, m_cap, workspace=None):
 
 def _indices(T, E, k, seed):
     g = torch.Generator().manual_seed(seed)
+    if T == 0:
+        return torch.zeros((1, k), dtype=torch.int32)[:0]
     return torch.rand(T, E, generator=g).argsort(1)[:, :k].int().contiguous()
 
 
@@ -47,7 +49,10 @@ def test_static_route_plan_matches_workspace_version_twice(lib):
     torch.cuda.set_device(0)
     # first a large problem (fills much of the scratch), then a small one with
     # other shapes: left-over scratch contents must not leak into the result
-    for T, E, k, seed in [(8192, 32, 8, 5), (300, 64, 6, 6)]:
+    # ... then exactly at the limit of the built-in scratch (ceil(T*k/256)*E ==
+    # 131072 entries) and a call without tokens
+    assert (8192 * 8 // 256) * 512 == lib.moeb_route_plan_static_max_ints()
+    for T, E, k, seed in [(8192, 32, 8, 5), (300, 64, 6, 6), (8192, 512, 8, 7), (0, 256, 8, 8)]:
         idx = _indices(T, E, k, seed).to(DEV)
         m_cap = lib.moeb_route_plan_rows(T, k, E, 128)
         ws = torch.empty(lib.moeb_route_plan_workspace_bytes(T, k, E), dtype=torch.uint8, device=DEV)

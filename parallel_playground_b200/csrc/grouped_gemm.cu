@@ -79,7 +79,7 @@ static_assert(kGemmSmemBytesScatter <= 232448, "shared memory per CTA");
 constexpr int kSwigluRowPitch = 144;
 constexpr int kGemmSmemBytesSwiglu = kGemmSmemBytes + 128 * kSwigluRowPitch;
 
-enum Role { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3 };
+enum Role { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3, kRoleStore = 5 };
 
 struct GemmParams {
   const float* scale_a;   // [K/128, m_total]
@@ -206,6 +206,29 @@ __device__ __forceinline__ void tmem_wait_ld_fence(uint32_t (&v)[32]) {
       : "memory");
 }
 
+// Bulk asynchronous copy shared -> global (local or peer memory): both addresses
+// 16-byte aligned, size a multiple of 16 bytes. Completion is tracked per thread
+// through bulk groups.
+__device__ __forceinline__ void bulk_store_s2g(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+               "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_group0() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 // acc[kOffset/2 .. kOffset/2+16) += v[0..32) * m, accumulators kept as float2 pairs
 template <int kOffset>
 __device__ __forceinline__ void fma_chunk(float2 (&acc)[64], const uint32_t (&v)[32], float m) {
@@ -216,12 +239,26 @@ __device__ __forceinline__ void fma_chunk(float2 (&acc)[64], const uint32_t (&v)
   }
 }
 
-template <bool kSwiglu, bool kScatter = false>
+// kOffload: the finished tile leaves the SM through a store warp. The promotion
+// warps only stage it in shared memory and signal an mbarrier; warp 2 (gate/up;
+// warps 2 and 3, one per column half, for the down projection) then issues one
+// bulk asynchronous copy (cp.async.bulk shared -> global) per row, to local
+// memory or straight to a peer GPU, while the promotion warps are already in the
+// next tile's K loop. Without it the promotion warps copy the tile out themselves.
+// kOpt bits: kOptOffload (above); kOptEarly: open the next tile (first scales,
+// layout word) before the epilogue instead of after it; kOptTanh: SiLU through one
+// tanh.approx instead of ex2 + rcp (half the special-function work of the SwiGLU
+// epilogue).
+constexpr int kOptOffload = 1, kOptEarly = 2, kOptTanh = 4;
+template <bool kSwiglu, bool kScatter = false, int kOpt = 0>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
                         const __grid_constant__ CUtensorMap tm_b0,
                         const __grid_constant__ CUtensorMap tm_b1, const GemmParams p) {
   constexpr int kSt = kScatter ? kStagesScatter : kStages;  // pipeline stages
+  constexpr bool kOffload = (kOpt & kOptOffload) != 0;
+  constexpr bool kEarly = (kOpt & kOptEarly) != 0;
+  constexpr bool kTanh = (kOpt & kOptTanh) != 0;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -236,6 +273,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 8 * (2 * kSt + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* amax_x = reinterpret_cast<float*>(aux + 256);  // [2 tile parities][2 halves][128 rows]
+  // hand-off of the staged output tile to the store warp(s) (kOffload)
+  auto staged_bar = [&](int h) { return bar_base + 3072u + 8u * h; };
+  auto stage_free_bar = [&](int h) { return bar_base + 3072u + 16u + 8u * h; };
   // output staging: row-store epilogue of the down projection (kScatter), or the
   // 128 x 128-byte tile of the gate/up kernel
   uint8_t* scatter_smem = aux + kSmemAux;
@@ -251,6 +291,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
     for (int b = 0; b < 2; ++b) {
       mbar_init(tmem_full_bar(b), 1);
       mbar_init(tmem_empty_bar(b), kEpiWarps);
+    }
+    if constexpr (kOffload) {
+      // gate/up: all eight promotion warps stage one tile; down: four per column half
+      mbar_init(staged_bar(0), kSwiglu ? kEpiWarps : kEpiWarps / 2);
+      mbar_init(staged_bar(1), kEpiWarps / 2);
+      mbar_init(stage_free_bar(0), 1);
+      mbar_init(stage_free_bar(1), 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -352,6 +399,50 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
           if (buf == 0) bphase ^= 1u;
         }
       }
+    } else if (kOffload && (warp == 2 || (!kSwiglu && warp == 3))) {
+      // ------------------------------------------------------- store warp --
+      // Takes every staged tile (gate/up) or column half (down) out of shared
+      // memory: one bulk asynchronous copy per row, lane l owns rows l, l+32,
+      // l+64, l+96. Down projection: one warp per column half (warps 2 and 3).
+      const int h = warp - 2;
+      uint32_t sphase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const TileInfo ti = get_tile(p, tile);
+        if (!ti.valid) continue;
+        if (!mbar_wait_bounded(staged_bar(h), sphase, abort_flag, p.wait_hint_ns)) {
+          if (lane == 0) report_timeout(p.status, kRoleStore, tile, -1);
+          break;
+        }
+        if constexpr (kSwiglu) {
+          uint8_t* out_tile = reinterpret_cast<uint8_t*>(p.out) + (size_t)ti.n_block * 128;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = lane + 32 * i;
+            const int grow = ti.m_block * kBM + r;
+            if (grow < p.m_total)
+              bulk_store_s2g(out_tile + (size_t)grow * p.N,
+                             smem_u32(scatter_smem + r * kSwigluRowPitch), 128);
+          }
+        } else {
+          const uint8_t* stage = scatter_smem + h * kScatterWgBytes;
+          const uint64_t* row_dst =
+              reinterpret_cast<const uint64_t*>(stage + 128 * kScatterRowPitch);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = lane + 32 * i;
+            const uint64_t d = row_dst[r];
+            if (d != 0)
+              bulk_store_s2g(reinterpret_cast<void*>(d), smem_u32(stage + r * kScatterRowPitch),
+                             256);
+          }
+        }
+        bulk_commit_group();
+        bulk_wait_group_read0();   // the staging area has been read: it may be rewritten
+        __syncwarp();
+        if (lane == 0) mbar_arrive(stage_free_bar(h));
+        sphase ^= 1u;
+      }
+      bulk_wait_group0();          // every row has reached global memory
     }
   } else {
     // ------------------------------------------- promotion + epilogue warps --
@@ -363,12 +454,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
     int buf = 0;
     uint32_t bphase = 0;
     int tile_parity = 0;
+    uint32_t sphase = 0;  // phase of the staging hand-off (kOffload)
     bool ok = true;
     const int n_scale_blocks = p.N / 128;
     // Measured on B200: asking for the next tile's layout word one tile early
     // pays off for the gate/up kernel (long K loop, -16 %), not for the down
     // kernel (short K loop), which keeps the plain tile loop.
-    constexpr bool kTileLookAhead = kSwiglu;
+    constexpr bool kTileLookAhead = kSwiglu || kOffload;
     // Per-tile addresses of this thread's scales, and the values a tile needs
     // first (scales of K block 0, layout word of the row).
     struct EpiTile {
@@ -438,6 +530,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       const float* sa_run = sa_ptr + p.m_total;
       const float* sb_run = sb0_ptr + 1;
       const ptrdiff_t sb_delta = sb1_ptr - sb0_ptr;
+      // kept rolled: unrolled by two the loop was measured 17 % slower on B200
+#pragma unroll 1
       for (int kb = 0; kb < num_kb; ++kb) {
         const float m0 = sa_next * sb0_next;
         const float m1 = sa_next * sb1_next;
@@ -486,6 +580,19 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       if (!ok) break;
 
+      // With the store warp (kOffload) the next tile is opened before the epilogue:
+      // its layout word was requested a tile ago, and the first scales it needs are
+      // in flight while this tile's epilogue runs.
+      // Down projection: the next tile is opened before the epilogue, so that the
+      // first scales it needs are in flight while this tile is converted and staged.
+      // Gate/up: the same, but only after the SwiGLU loop, when the registers of the
+      // `up` accumulators are free (opened earlier, the extra live values spill).
+      EpiTile et_next{};
+      if constexpr (kTileLookAhead && kEarly && !kSwiglu) {
+        w.advance(p, num_tiles);
+        if (w.tile < num_tiles) et_next = open_tile(w.ti);
+      }
+
       // ------------------------------------------------------- tile epilogue --
       bool row_ok = row < p.m_total;
       if (row_ok) {
@@ -498,9 +605,20 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
           const float g = ACC(i);
-          const float y = __fdividef(ACC(64 + i) * g, 1.0f + __expf(-g));
+          float y;
+          if constexpr (kTanh) {
+            // g * sigmoid(g) = hg * (tanh(hg) + 1) with hg = g / 2
+            const float hg = 0.5f * g;
+            y = ACC(64 + i) * fmaf(hg, tanh_approx(hg), hg);
+          } else {
+            y = __fdividef(ACC(64 + i) * g, 1.0f + __expf(-g));
+          }
           ACC(i) = y;
           amax = fmaxf(amax, fabsf(y));
+        }
+        if constexpr (kTileLookAhead && kEarly) {
+          w.advance(p, num_tiles);
+          if (w.tile < num_tiles) et_next = open_tile(w.ti);
         }
         float* xchg = amax_x + tile_parity * 256;
         xchg[h * 128 + row_in_tile] = amax;
@@ -511,6 +629,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
         // one reciprocal per row instead of 64 IEEE divisions; the conversion
         // saturates to +-448, which is the clamp
         const float inv = amax > 0.0f ? __fdiv_rn(kFp8Max, amax) : 1.0f;
+        if constexpr (kOffload) {
+          // the store warp has taken the previous tile out of the staging area
+          if (!mbar_wait_bounded(stage_free_bar(0), sphase ^ 1u, abort_flag, p.wait_hint_ns)) {
+            if (lane == 0) report_timeout(p.status, kRoleEpilogue, tile, -2);
+            break;
+          }
+        }
         if (row < p.m_total) {
           uint32_t packed[16];
 #pragma unroll
@@ -527,6 +652,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
                 make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
           if (h == 0) p.scale_d[(size_t)ti.n_block * p.m_total + row] = s;
         }
+        if constexpr (kOffload) {
+          // hand the staged tile to the store warp and go on with the next tile
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(staged_bar(0));
+          sphase ^= 1u;
+        } else {
         // both warpgroups have staged their halves: every row (128 bytes) goes out
         // as one run, eight lanes per row
         named_barrier_sync(3, kEpiThreads);
@@ -542,6 +674,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
               *reinterpret_cast<uint4*>(out_tile + (size_t)grow * p.N + part * 16) =
                   *reinterpret_cast<const uint4*>(scatter_smem + r * kSwigluRowPitch + part * 16);
           }
+        }
         }
         tile_parity ^= 1;
       } else {
@@ -568,6 +701,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
           const bool local = p.scatter_out == nullptr;
           if (local && row < p.m_total && col0 < p.N)
             my_dst = reinterpret_cast<uint64_t>(p.out) + ((size_t)row * p.N + col0) * 2;
+          if constexpr (kOffload) {
+            // the store warp has taken the previous tile out of this half's staging area
+            if (!mbar_wait_bounded(stage_free_bar(h), sphase ^ 1u, abort_flag, p.wait_hint_ns)) {
+              if (lane == 0) report_timeout(p.status, kRoleEpilogue, tile, -2);
+              break;
+            }
+          }
           row_dst[row_in_tile] = my_dst;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -580,6 +720,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
             *reinterpret_cast<uint4*>(stage + row_in_tile * kScatterRowPitch + 16 * i) =
                 make_uint4(wv[0], wv[1], wv[2], wv[3]);
           }
+          if constexpr (kOffload) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(staged_bar(h));
+            sphase ^= 1u;
+          } else {
           named_barrier_sync(2 + h, 128);
           // 128 rows x 16 sixteen-byte pieces; consecutive lanes take consecutive pieces
 #pragma unroll 4
@@ -595,6 +741,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
           // the staging area is reused by this warpgroup's next tile
           named_barrier_sync(2 + h, 128);
+          }
         } else
         if (row < p.m_total && col0 < p.N) {
           if (p.out_f32) {
@@ -625,7 +772,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
         }
       }
-      if constexpr (kTileLookAhead) {
+      if constexpr (kTileLookAhead && kEarly) {
+        et = et_next;
+        tile = w.tile;
+      } else if constexpr (kTileLookAhead) {
         // next tile (its layout word was requested at the start of this one)
         w.advance(p, num_tiles);
         if (w.tile < num_tiles) et = open_tile(w.ti);
@@ -988,14 +1138,25 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
   p.num_n_blocks = kSwiglu ? p.N / 128 : ceil_div(p.N, 256);
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const GemmParams);
+  // Measured on B200 (one launch each, default workload): gate/up with the tanh
+  // form of SiLU 0.842 ms against 0.852; the store warp or an earlier opening of
+  // the next tile make gate/up slower (0.87 / 1.02 ms) and are not used there; down
+  // projection with store warps and the early opening 0.456 ms against 0.508.
+  // MOEB_GEMM_PLAIN=1 selects the forms without these options (comparison runs).
+  static const bool plain = [] {
+    const char* e = getenv("MOEB_GEMM_PLAIN");
+    return e && e[0] == '1';
+  }();
   KernelFn kernel = grouped_gemm_fp8_kernel<kSwiglu>;
   int smem_bytes = kSwiglu ? kGemmSmemBytesSwiglu : kGemmSmemBytes;
-  if constexpr (!kSwiglu) {
-    // bf16 output, local or to peers: the staged row-store epilogue (measured 13 %
-    // faster than per-thread row pieces also for local rows); f32 output keeps the
-    // plain epilogue
+  if constexpr (kSwiglu) {
+    if (!plain) kernel = grouped_gemm_fp8_kernel<true, false, kOptTanh>;
+  } else {
+    // bf16 output, local or to peers: rows are staged in shared memory and leave
+    // the SM whole; f32 output keeps the plain epilogue
     if (p.scatter_out != nullptr || !p.out_f32) {
-      kernel = grouped_gemm_fp8_kernel<false, true>;
+      kernel = plain ? grouped_gemm_fp8_kernel<false, true, 0>
+                     : grouped_gemm_fp8_kernel<false, true, kOptOffload | kOptEarly>;
       smem_bytes = kGemmSmemBytesScatter;
     }
   }

@@ -192,8 +192,8 @@ int moeb_gather_rows_bf16(const void *y_bf16, const int32_t *row_of, int n, int 
  * quantises every token once and stores its k copies directly into the owners'
  * buffers, moeb_ep_combine_pull reads the k expert outputs back from the owners
  * and reduces them. peer_* are device arrays of W buffer base addresses (this
- * rank's own buffer included); the caller synchronises the ranks between the
- * phases (stream-ordered collectives).
+ * rank's own buffer included); the caller lets the ranks meet between the phases
+ * with moeb_ep_barrier (stream-ordered, no host wait).
  *   counts_all [W,E] int32; dest_base [E]; m_valid [1] = this rank's padded rows;
  *   send_row / send_offsets: moeb_route_plan(pad = 1) outputs dst_row / padded_offsets;
  *   peer_x[d]: e4m3 [m_cap,H]; peer_scale[d]: fp32 [m_cap, H/128] (row-major staging,
@@ -357,6 +357,141 @@ int moeb_moe_forward_host(const moeb_layer_config *cfg, const void *x_bf16_host,
                           const void *up_q, const float *up_scale, const void *down_q,
                           const float *down_scale, void *workspace, size_t workspace_bytes,
                           int32_t *status_dev, void *stream);
+
+/* ---- expert-parallel context: dispatch, combine and the EP layer as single calls ----
+ * Replaces, for W > 1 ranks, All2All / All2AllBase and their context and worker
+ * (csrc/all2all/all2all_base.hpp:11-52, all2all_tk.hpp:201-394, a2a_context_tk.hpp:66-178,
+ * a2a_worker_tk.hpp:163-384), naive_moe_forward (src/moe_ops.cu:153-191) and the fused
+ * dispatch + gate/up GEMM of kernel5_1 (csrc/tk_bindings.cu:17-60,
+ * moe_cuda/include/moe_cuda/kernels/kernel5_1.cuh:448-778). One process per GPU.
+ *
+ * Memory comes from the caller:
+ *   - one SYMMETRIC buffer per rank of moeb_ep_symmetric_bytes(cfg) bytes, 256-byte
+ *     aligned, mapped into every rank's address space (CUDA VMM handles, IPC, torch
+ *     symmetric memory: what the reference gets from TKParallelTensor); peer_base_host[p]
+ *     is the address of rank p's buffer as THIS process sees it (host array of W words);
+ *   - a LOCAL workspace of moeb_ep_local_bytes(cfg) bytes, 256-byte aligned.
+ * moeb_ep_create clears the flag words of this rank's symmetric buffer and returns after
+ * its stream work is done; the caller must let EVERY rank finish moeb_ep_create before any
+ * rank dispatches (one host-side barrier at set-up; none afterwards).
+ *
+ * Transport. A rank quantises its tokens once (e4m3, 1x128 scales) into its symmetric
+ * buffer; the per-expert counts travel with a rank-barrier kernel; every expert copy costs
+ * its sender one 8-byte word stored into the owner's buffer; the owners load the rows over
+ * NVLink (plain peer loads, no TMA multicast), either in a kernel of their own or, in the
+ * fused form, by a few comm CTAs of the gate/up GEMM while its other CTAs already compute
+ * on the 128-row blocks that have landed. Expert outputs go home inside the down GEMM's
+ * store warps, then one rank barrier and a local weighted reduction. Rows of an expert are
+ * ordered (source rank, token, slot). Every device-side wait is bounded (2 s), after which
+ * status_dev gets {4, role, index, tag} and the kernels run to their end.
+ * One dispatch/combine pair in flight per context (all2all_tk.hpp:31-32). */
+typedef struct {
+  int max_tokens;      /* tokens a rank brings to one dispatch, at most */
+  int hidden;          /* H, multiple of 128 */
+  int num_experts;     /* E over all ranks, multiple of world; rank r owns experts [r*E/W, (r+1)*E/W) */
+  int top_k;           /* experts per token, <= 32 */
+  int expert_padding;  /* every local expert's rows start on a multiple of this (128) */
+  int world, rank;
+  int capacity_rows;   /* rows a rank can receive; 0 = worst case (all2all_tk.hpp:101-106) */
+} moeb_ep_config;
+
+typedef struct moeb_ep_ctx moeb_ep_ctx;
+
+/* What a rank holds after a dispatch (device pointers into the local workspace / this
+ * rank's symmetric buffer; valid until moeb_ep_destroy). */
+typedef struct {
+  void *expert_x;              /* e4m3 [max_recv_rows, H] */
+  float *expert_x_scale;       /* fp32 [H/128, max_recv_rows], MN-major */
+  int32_t *grouped_layout;     /* [max_recv_rows] local expert id per row, -1 padding */
+  int32_t *m_valid;            /* [1] padded rows in use */
+  int32_t *tokens_per_expert;  /* [E/W] unpadded rows per local expert */
+  int32_t *padded_offsets;     /* [E/W + 1] */
+  int32_t *source_rank;        /* [max_recv_rows] rank a row came from, -1 padding */
+  int32_t *source_pos;         /* [max_recv_rows] token*k + slot on that rank (after the receive half) */
+  int32_t *dst_rank, *dst_row; /* [T, k] where this rank's copies went, -1 if dropped */
+  int32_t *overflow;           /* [1] copies dropped because the owner's capacity_rows was too small */
+  void *home;                  /* bf16 [max_tokens*k, H]: expert outputs of this rank's tokens */
+  int max_recv_rows, local_experts;
+  int rows;                    /* rows of expert_x (= max_recv_rows) */
+} moeb_ep_view;
+
+int moeb_ep_max_recv_rows(const moeb_ep_config *cfg);
+size_t moeb_ep_symmetric_bytes(const moeb_ep_config *cfg);
+size_t moeb_ep_local_bytes(const moeb_ep_config *cfg);
+int moeb_ep_create(const moeb_ep_config *cfg, const uint64_t *peer_base_host,
+                   void *local_workspace, size_t local_bytes, void *stream, moeb_ep_ctx **out);
+int moeb_ep_destroy(moeb_ep_ctx *ctx);
+int moeb_ep_get_view(moeb_ep_ctx *ctx, moeb_ep_view *view);
+
+/* All2All::dispatch (all2all_tk.hpp:201-334). Tokens are either bf16 [T,H] (x_bf16; they
+ * are quantised here) or already quantised as the reference passes them (x_q e4m3 [T,H] +
+ * x_scale_mn fp32 [H/128, T]); indices int32 [T,k]. do_send / do_recv are the two halves of
+ * the reference (:292-334): the send half quantises, plans, exchanges the counts and
+ * announces the copies; the receive half fetches the rows. After the send half the layout
+ * fields of the view are valid, after the receive half expert_x / expert_x_scale /
+ * source_pos as well. The rows land in out_expert_x (e4m3 [out_rows, H]) /
+ * out_expert_x_scale (fp32 [H/128, out_rows]) with out_rows == max_recv_rows, or, when both
+ * are NULL, in buffers of the context (see the view). status_dev: optional int32[4]. */
+int moeb_ep_dispatch(moeb_ep_ctx *ctx, const void *x_bf16, const void *x_q,
+                     const float *x_scale_mn, const int32_t *indices, int num_tokens,
+                     void *out_expert_x, float *out_expert_x_scale, int out_rows, int do_send,
+                     int do_recv, int32_t *status_dev, void *stream);
+
+/* All2All::combine (all2all_tk.hpp:336-394): send half: every row of expert_y (bf16
+ * [max_recv_rows, H]) goes to its source rank's home buffer; receive half: rank barrier,
+ * then out[t] = (accumulate ? out[t] : 0) + sum_j weights[t,j] * home[t*k+j] in slot order. */
+int moeb_ep_combine(moeb_ep_ctx *ctx, const void *expert_y_bf16, const float *weights,
+                    void *out_bf16, int accumulate, int do_send, int do_recv,
+                    int32_t *status_dev, void *stream);
+
+/* fused_dispatch_grouped_gemm_swiglu (csrc/tk_bindings.cu:17-60): dispatch and the
+ * gate/up + SwiGLU + re-quantisation GEMM over what arrives, in one call. Token and output
+ * arguments as moeb_ep_dispatch; gate/up e4m3 [E/W, I, H] with 128x128 scales; D e4m3
+ * [max_recv_rows, I], scale_d fp32 [I/128, max_recv_rows]. fused != 0: a few comm CTAs of
+ * the GEMM kernel fetch the rows while the others compute on the 128-row blocks that have
+ * arrived (kernel5_1.cuh:274-285, 698-758); fused == 0: the rows are fetched by a kernel of
+ * their own first. Same bits either way. */
+int moeb_ep_fused_dispatch_swiglu(moeb_ep_ctx *ctx, const void *x_bf16, const void *x_q,
+                                  const float *x_scale_mn, const int32_t *indices,
+                                  int num_tokens, void *out_expert_x, float *out_expert_x_scale,
+                                  int out_rows, const void *gate_q, const float *gate_scale,
+                                  const void *up_q, const float *up_scale, void *D, float *scale_d,
+                                  int intermediate, int fused, int32_t *status_dev, void *stream);
+
+/* fused_grouped_gemm_combine (csrc/tk_bindings.cu:62-94; the reference ships the launcher
+ * only, csrc/jit_kernels/impls/kernel5_2.hpp:125-220): the down projection of A (e4m3
+ * [max_recv_rows, I], scale_a fp32 [I/128, max_recv_rows]) whose store warps send every row
+ * to its source rank, then the rank barrier and the weighted reduction into out_bf16 [T, H].
+ * status_dev: optional int32[8] (GEMM, barrier). */
+int moeb_ep_fused_gemm_combine(moeb_ep_ctx *ctx, const void *A, const float *scale_a,
+                               const void *down_q, const float *down_scale, int intermediate,
+                               const float *weights, void *out_bf16, int accumulate,
+                               int32_t *status_dev, void *stream);
+
+/* The whole layer on W ranks in one call: router -> dispatch -> gate/up + SwiGLU GEMM ->
+ * down GEMM (rows sent home by its store warps) -> barrier -> weighted reduction
+ * (naive_moe_forward_dispatch, csrc/python_api.cpp:516-532, with the router in front).
+ * cfg->H/E/k must match the context, cfg->T <= max_tokens; gate/up [E/W,I,H], down
+ * [E/W,H,I] hold this rank's experts. fused != 0: the dispatch's receive half runs inside
+ * the gate/up GEMM (kernel5_1 semantics), else as a kernel of its own before it; both give
+ * the same bits. workspace: moeb_ep_moe_forward_workspace_bytes(ctx, I) bytes, 256-byte
+ * aligned. status_dev: optional int32[12] (gate/up GEMM, down GEMM, rank barrier / pull). */
+size_t moeb_ep_moe_forward_workspace_bytes(const moeb_ep_ctx *ctx, int intermediate);
+int moeb_ep_moe_forward(moeb_ep_ctx *ctx, const moeb_layer_config *cfg, const void *x_bf16,
+                        const void *w_router_bf16, const float *router_bias, const void *gate_q,
+                        const float *gate_scale, const void *up_q, const float *up_scale,
+                        const void *down_q, const float *down_scale, void *out_bf16,
+                        int32_t *indices_out, float *weights_out, void *workspace,
+                        size_t workspace_bytes, int fused, int32_t *status_dev, void *stream);
+
+/* Optional stage timing of moeb_ep_moe_forward with CUDA events owned by the context (the
+ * reference brackets its launches with NVTX ranges, csrc/runtime/utils.h:7-15): after
+ * moeb_ep_set_timing(ctx, 1) up to 64 calls are recorded; moeb_ep_read_timing (after the
+ * stream has been synchronised) returns the mean milliseconds of {router, dispatch send
+ * half, gate/up GEMM incl. the receive half, down GEMM, barrier + reduction} and the number
+ * of calls, and starts a new series. */
+int moeb_ep_set_timing(moeb_ep_ctx *ctx, int enable);
+int moeb_ep_read_timing(moeb_ep_ctx *ctx, float *stage_ms5, int *steps);
 
 #ifdef __cplusplus
 }

@@ -20,7 +20,7 @@ CSRC = PKG_DIR / "csrc"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libmoe_cuda_b200.so"
 
-SOURCES = ["api.cu", "router.cu", "route_plan.cu", "quant.cu", "combine.cu", "ep_p2p.cu",
+SOURCES = ["api.cu", "router.cu", "route_plan.cu", "quant.cu", "combine.cu", "ep_p2p.cu", "ep_ctx.cu",
            "grouped_gemm.cu"]
 
 NVCC_FLAGS = [

@@ -38,6 +38,23 @@ class MoebError(RuntimeError):
         self.status = status
 
 
+class EpConfig(ctypes.Structure):
+    """moeb_ep_config"""
+    _fields_ = [("max_tokens", c_int), ("hidden", c_int), ("num_experts", c_int),
+                ("top_k", c_int), ("expert_padding", c_int), ("world", c_int), ("rank", c_int),
+                ("capacity_rows", c_int)]
+
+
+class EpView(ctypes.Structure):
+    """moeb_ep_view"""
+    _fields_ = [("expert_x", c_void_p), ("expert_x_scale", c_void_p), ("grouped_layout", c_void_p),
+                ("m_valid", c_void_p), ("tokens_per_expert", c_void_p),
+                ("padded_offsets", c_void_p), ("source_rank", c_void_p), ("source_pos", c_void_p),
+                ("dst_rank", c_void_p), ("dst_row", c_void_p), ("overflow", c_void_p),
+                ("home", c_void_p), ("max_recv_rows", c_int), ("local_experts", c_int),
+                ("rows", c_int)]
+
+
 # name -> (restype, argtypes); every symbol include/moe_cuda_b200.h declares
 PROTOTYPES = {
     "moeb_abi_version": (c_int, []),
@@ -115,6 +132,30 @@ PROTOTYPES = {
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
                                       c_void_p]),
+    "moeb_ep_max_recv_rows": (c_int, [ctypes.POINTER(EpConfig)]),
+    "moeb_ep_symmetric_bytes": (c_size_t, [ctypes.POINTER(EpConfig)]),
+    "moeb_ep_local_bytes": (c_size_t, [ctypes.POINTER(EpConfig)]),
+    "moeb_ep_create": (c_int, [ctypes.POINTER(EpConfig), c_void_p, c_void_p, c_size_t, c_void_p,
+                               ctypes.POINTER(c_void_p)]),
+    "moeb_ep_destroy": (c_int, [c_void_p]),
+    "moeb_ep_get_view": (c_int, [c_void_p, ctypes.POINTER(EpView)]),
+    "moeb_ep_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "moeb_ep_fused_dispatch_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                              c_void_p, c_void_p]),
+    "moeb_ep_fused_gemm_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                           c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "moeb_ep_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                c_void_p, c_void_p]),
+    "moeb_ep_moe_forward_workspace_bytes": (c_size_t, [c_void_p, c_int]),
+    "moeb_ep_moe_forward": (c_int, [c_void_p, ctypes.POINTER(LayerConfig), c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                    c_int, c_void_p, c_void_p]),
+    "moeb_ep_set_timing": (c_int, [c_void_p, c_int]),
+    "moeb_ep_read_timing": (c_int, [c_void_p, ctypes.POINTER(c_float), ctypes.POINTER(c_int)]),
 }
 
 _lib = None

@@ -13,10 +13,11 @@
 //             buffers (16-byte peer loads) and reduces them with its weights.
 // Destination rows follow from the all-gathered per-expert counts, so the row
 // order is the same deterministic one as everywhere else: (expert, source rank,
-// token, slot). Ranks synchronise between the phases with stream-ordered
-// collectives issued by the host side; these kernels never wait on a peer.
+// token, slot). Ranks meet between the phases in ep_barrier_kernel (flag words in
+// peer memory, bounded wait); the data kernels themselves never wait on a peer.
 // Peer buffers are addressed through a device array of W base addresses.
 #include "common.cuh"
+#include "ep_pull.cuh"
 #include "moe_cuda_b200.h"
 
 namespace moeb {
@@ -322,7 +323,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 }
 
 __global__ void __launch_bounds__(kBarrierThreads)
-ep_barrier_kernel(const uint64_t* __restrict__ peer_flags, const uint64_t* __restrict__ peer_counts,
+ep_barrier_kernel(const uint64_t* __restrict__ peer_flags, size_t flags_off,
+                  const uint64_t* __restrict__ peer_counts,
                   const int32_t* __restrict__ my_counts, int n_counts, int rank, int W,
                   int channel, uint32_t epoch, int32_t* __restrict__ status) {
   if (peer_counts != nullptr) {
@@ -335,10 +337,11 @@ ep_barrier_kernel(const uint64_t* __restrict__ peer_flags, const uint64_t* __res
   __syncthreads();
   if ((int)threadIdx.x < W) {
     const int p = threadIdx.x;
-    uint32_t* theirs = reinterpret_cast<uint32_t*>(peer_flags[p]) + (size_t)channel * W + rank;
+    uint32_t* theirs =
+        reinterpret_cast<uint32_t*>(peer_flags[p] + flags_off) + (size_t)channel * W + rank;
     st_release_sys_u32(theirs, epoch);
     const uint32_t* mine =
-        reinterpret_cast<const uint32_t*>(peer_flags[rank]) + (size_t)channel * W + p;
+        reinterpret_cast<const uint32_t*>(peer_flags[rank] + flags_off) + (size_t)channel * W + p;
     const uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
     while ((int32_t)(ld_acquire_sys_u32(mine) - epoch) < 0) {
@@ -478,7 +481,17 @@ extern "C" int moeb_ep_barrier(const uint64_t* peer_flags, const uint64_t* peer_
     return kInvalidArgument;
   }
   ep_barrier_kernel<<<1, kBarrierThreads, 0, (cudaStream_t)stream>>>(
-      peer_flags, peer_counts, my_counts, n_counts, rank, W, channel, epoch, status_dev);
+      peer_flags, 0, peer_counts, my_counts, n_counts, rank, W, channel, epoch, status_dev);
+  MOEB_CUDA_TRY(cudaGetLastError());
+  return kOk;
+}
+
+// The same barrier over flag words that lie `flags_off` bytes into every rank's
+// symmetric buffer (peer_base: the W buffer base addresses); no payload.
+int moeb::ep_barrier_off(const uint64_t* peer_base, size_t flags_off, int rank, int W, int channel,
+                         uint32_t epoch, int32_t* status_dev, cudaStream_t stream) {
+  ep_barrier_kernel<<<1, kBarrierThreads, 0, stream>>>(peer_base, flags_off, nullptr, nullptr, 0,
+                                                       rank, W, channel, epoch, status_dev);
   MOEB_CUDA_TRY(cudaGetLastError());
   return kOk;
 }

@@ -32,6 +32,7 @@
 // from grouped_layout, so no host-side knowledge of the per-expert counts is
 // needed and padding-only blocks are skipped.
 #include "common.cuh"
+#include "ep_pull.cuh"
 #include "moe_cuda_b200.h"
 
 #include <cstdio>
@@ -97,9 +98,17 @@ struct GemmParams {
   // GEMM): row r is stored to peer buffer scatter_out[scatter_rank[r]] at row
   // scatter_pos[r] instead of out[r]
   const uint64_t* scatter_out;
+  size_t scatter_off;  // byte offset of the destination buffer behind every base address
   const int32_t* scatter_rank;
   const int32_t* scatter_pos;
   uint32_t wait_hint_ns;  // suspend-time hint of the mbarrier waits (0 = plain polling)
+  // Fused dispatch (kOptFused): the last n_comm CTAs pull this rank's rows from
+  // their source ranks (ep_pull.cuh) and count them per 128-row block; the other
+  // CTAs run the GEMM and wait for a block's rows before they load it.
+  const int32_t* arrive_cnt;   // [num_m_blocks] rows landed so far
+  const int32_t* arrive_need;  // [num_m_blocks] rows the block holds
+  int n_comm;
+  PullParams pull;
 };
 
 struct TileInfo {
@@ -159,10 +168,10 @@ __device__ __forceinline__ TileInfo get_tile(const GemmParams& p, int tile) {
 // tile is requested while the current tile is processed, so that the global
 // load latency is not paid at every tile boundary.
 struct TileWalker {
-  int tile, cand, cand_key;
+  int tile, cand, cand_key, stride;
   TileInfo ti;
   __device__ __forceinline__ void prefetch(const GemmParams& p, int num_tiles) {
-    cand = tile + (int)gridDim.x;
+    cand = tile + stride;
     cand_key = cand < num_tiles ? __ldg(p.layout + tile_key_index(p, cand)) : 0;
   }
   // first valid tile at or after `start`
@@ -172,7 +181,7 @@ struct TileWalker {
     while (tile < num_tiles) {
       ti = make_tile(p, tile, __ldg(p.layout + tile_key_index(p, tile)));
       if (ti.valid) break;
-      tile += (int)gridDim.x;
+      tile += stride;
     }
   }
   // move to the next valid tile, using the prefetched word when it applies
@@ -184,7 +193,7 @@ struct TileWalker {
         ti = c;
         return;
       }
-      seek(p, cand + (int)gridDim.x, num_tiles);
+      seek(p, cand + stride, num_tiles);
     } else {
       tile = num_tiles;
       ti.valid = false;
@@ -249,7 +258,29 @@ __device__ __forceinline__ void fma_chunk(float2 (&acc)[64], const uint32_t (&v)
 // layout word) before the epilogue instead of after it; kOptTanh: SiLU through one
 // tanh.approx instead of ex2 + rcp (half the special-function work of the SwiGLU
 // epilogue).
-constexpr int kOptOffload = 1, kOptEarly = 2, kOptTanh = 4;
+// kOptFused: dispatch fused into the GEMM (see GemmParams::arrive_cnt).
+constexpr int kOptOffload = 1, kOptEarly = 2, kOptTanh = 4, kOptFused = 8;
+// Fused dispatch: wait (bounded) until all rows of a 128-row block have been
+// published by the comm CTAs. Every lane of the warp polls the same word.
+__device__ __forceinline__ bool wait_rows_arrived(const GemmParams& p, int m_block,
+                                                  volatile int* abort_flag) {
+  const int need = __ldg(p.arrive_need + m_block);
+  if (ld_acquire_gpu_s32(p.arrive_cnt + m_block) >= need) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_gpu_s32(p.arrive_cnt + m_block) < need) {
+    if ((++spins & 15u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > kPullLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+    __nanosleep(100);
+  }
+  return true;
+}
+
 template <bool kSwiglu, bool kScatter = false, int kOpt = 0>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
@@ -259,6 +290,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
   constexpr bool kOffload = (kOpt & kOptOffload) != 0;
   constexpr bool kEarly = (kOpt & kOptEarly) != 0;
   constexpr bool kTanh = (kOpt & kOptTanh) != 0;
+  constexpr bool kFused = (kOpt & kOptFused) != 0;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -322,8 +354,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (p.m_valid != nullptr) num_m_blocks = min(num_m_blocks, ceil_div(max(__ldg(p.m_valid), 0), kBM));
   const int num_tiles = num_m_blocks * p.num_n_blocks;
   const int num_kb = p.K / kBK;
+  // tiles are dealt round-robin to the CTAs that run the GEMM
+  const int tile_stride = (int)gridDim.x - (kFused ? p.n_comm : 0);
 
-  if (warp < 4) {
+  if (kFused && (int)blockIdx.x >= tile_stride) {
+    // ------------------------------------------------ comm CTA: pull rows --
+    pull_rows(p.pull, ((int)blockIdx.x - tile_stride) * (kGemmThreads / 32) + warp,
+              p.n_comm * (kGemmThreads / 32));
+  } else if (warp < 4) {
     setmaxnreg_dec<kRegsProducerWg>();
     if (warp == 0) {
       // ------------------------------------------------------ TMA producer --
@@ -332,12 +370,20 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       bool ok = true;
       // (the producer and MMA warps run on 40 registers: they use the plain tile
       // loop; only the promotion warps prefetch the next tile's layout word)
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_stride) {
         const TileInfo ti = get_tile(p, tile);
         if (!ti.valid) continue;
         const int a_row = ti.m_block * kBM;
         const int b_row0 = ti.g * p.N + (kSwiglu ? ti.n_block * 128 : ti.n_block * 256);
         const int b_row1 = kSwiglu ? b_row0 : b_row0 + 128;
+        if constexpr (kFused) {
+          // the block's rows must have landed before the TMA unit reads them
+          if (!wait_rows_arrived(p, ti.m_block, abort_flag)) {
+            if (lane == 0) report_timeout(p.status, kRoleProducer, tile, -4);
+            break;
+          }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_hint_ns)) {
             if (lane == 0) report_timeout(p.status, kRoleProducer, tile, kb);
@@ -365,7 +411,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       int stage = 0, buf = 0;
       uint32_t phase = 0, bphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_stride) {
         const TileInfo ti = get_tile(p, tile);
         if (!ti.valid) continue;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -406,7 +452,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       // l+64, l+96. Down projection: one warp per column half (warps 2 and 3).
       const int h = warp - 2;
       uint32_t sphase = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < num_tiles; tile += tile_stride) {
         const TileInfo ti = get_tile(p, tile);
         if (!ti.valid) continue;
         if (!mbar_wait_bounded(staged_bar(h), sphase, abort_flag, p.wait_hint_ns)) {
@@ -470,6 +516,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
     };
     auto open_tile = [&](const TileInfo& t) {
       EpiTile e;
+      if constexpr (kFused) {
+        // the scales of the block are written by the comm CTAs: wait for them too
+        if (!wait_rows_arrived(p, t.m_block, abort_flag)) ok = false;
+      }
       e.row = t.m_block * kBM + row_in_tile;
       const int row_ld = e.row < p.m_total ? e.row : p.m_total - 1;
       int nb0;  // weight scale block for the first multiplier
@@ -491,6 +541,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       return e;
     };
     TileWalker w;
+    w.stride = tile_stride;
     EpiTile et{};
     int tile = blockIdx.x;
     if constexpr (kTileLookAhead) {
@@ -506,7 +557,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       } else {
         ti = get_tile(p, tile);
         if (!ti.valid) {
-          tile += gridDim.x;
+          tile += tile_stride;
           continue;
         }
         et = open_tile(ti);
@@ -693,7 +744,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
               const int src = __ldg(p.scatter_rank + row);
               const int pos = __ldg(p.scatter_pos + row);
               if (src >= 0 && pos >= 0)
-                my_dst = __ldg(p.scatter_out + src) + ((size_t)pos * p.N + col0) * 2;
+                my_dst = __ldg(p.scatter_out + src) + p.scatter_off + ((size_t)pos * p.N + col0) * 2;
             }
           }
           // local output: every row of the tile is written, rows that hold no
@@ -781,7 +832,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (w.tile < num_tiles) et = open_tile(w.ti);
         tile = w.tile;
       } else {
-        tile += gridDim.x;
+        tile += tile_stride;
       }
     }
   }
@@ -1149,8 +1200,14 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
   }();
   KernelFn kernel = grouped_gemm_fp8_kernel<kSwiglu>;
   int smem_bytes = kSwiglu ? kGemmSmemBytesSwiglu : kGemmSmemBytes;
+  int n_comm = 0;
   if constexpr (kSwiglu) {
     if (!plain) kernel = grouped_gemm_fp8_kernel<true, false, kOptTanh>;
+    if (p.arrive_cnt != nullptr) {
+      // dispatch fused into this launch: n_comm CTAs pull rows, the rest compute
+      kernel = grouped_gemm_fp8_kernel<true, false, kOptTanh | kOptFused>;
+      n_comm = p.n_comm;
+    }
   } else {
     // bf16 output, local or to peers: rows are staged in shared memory and leave
     // the SM whole; f32 output keeps the plain epilogue
@@ -1165,7 +1222,10 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
                                      smem_bytes));
   if (p.status) MOEB_CUDA_TRY(cudaMemsetAsync(p.status, 0, 4 * sizeof(int32_t), stream));
   const long long tiles = (long long)p.num_m_blocks * p.num_n_blocks;
-  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  // every CTA must be resident at once in the fused form (compute CTAs wait for
+  // comm CTAs): one CTA per SM, never more CTAs than SMs
+  const int compute_sms = sm_count() - n_comm;
+  const int grid = (int)(tiles < compute_sms ? tiles : compute_sms) + n_comm;
   kernel<<<grid, kGemmThreads, smem_bytes, stream>>>(tm_a, tm_b0, tm_b1, p);
   MOEB_CUDA_TRY(cudaGetLastError());
   return kOk;
@@ -1242,6 +1302,44 @@ extern "C" int moeb_fp8_grouped_gemm_swiglu_dyn(const void* A, const float* scal
   return launch_grouped_gemm<true>(A, gate, up, p, (cudaStream_t)stream);
 }
 
+// Gate/up GEMM with the dispatch fused in (used by the expert-parallel context,
+// ep_ctx.cu): contiguous layout, rows in use read from *m_valid_dev.
+int moeb::fp8_swiglu_fused_dispatch(const void* A, const float* scale_a, const void* gate,
+                                    const float* scale_gate, const void* up,
+                                    const float* scale_up, void* D, float* scale_d, int m_total,
+                                    const int32_t* m_valid_dev, int N, int K, int G,
+                                    const int32_t* grouped_layout, int32_t* status_dev,
+                                    const PullParams& pull, const int32_t* arrive_cnt,
+                                    const int32_t* arrive_need, int n_comm, cudaStream_t stream) {
+  int rc = check_common("fp8_swiglu_fused_dispatch", A, scale_a, gate, scale_gate, D, m_total, N, K,
+                        G, MOEB_GEMM_M_GROUPED_CONTIGUOUS, grouped_layout, 0);
+  if (rc != kOk) return rc;
+  if (!up || !scale_up || !scale_d || !aligned16(up) || !arrive_cnt || !arrive_need ||
+      !m_valid_dev || n_comm <= 0 || n_comm >= sm_count()) {
+    set_last_error_msg("fp8_swiglu_fused_dispatch: bad argument");
+    return kInvalidArgument;
+  }
+  GemmParams p{};
+  p.scale_a = scale_a;
+  p.scale_b0 = scale_gate;
+  p.scale_b1 = scale_up;
+  p.out = D;
+  p.scale_d = scale_d;
+  p.layout = grouped_layout;
+  p.status = status_dev;
+  p.m_total = m_total;
+  p.N = N;
+  p.K = K;
+  p.G = G;
+  p.m_valid = m_valid_dev;
+  p.arrive_cnt = arrive_cnt;
+  p.arrive_need = arrive_need;
+  p.n_comm = n_comm;
+  p.pull = pull;
+  p.pull.status = status_dev;
+  return launch_grouped_gemm<true>(A, gate, up, p, stream);
+}
+
 extern "C" int moeb_fp8_grouped_gemm_nt(const void* A, const float* scale_a, const void* W,
                                         const float* scale_w, void* out, int out_dtype,
                                         int m_total, int N, int K, int G, int gemm_type,
@@ -1288,6 +1386,17 @@ extern "C" int moeb_fp8_grouped_gemm_nt_scatter(const void* A, const float* scal
                                                 int m_total, const int32_t* m_valid_dev, int N,
                                                 int K, int G, const int32_t* grouped_layout,
                                                 int32_t* status_dev, void* stream) {
+  return moeb::fp8_gemm_nt_scatter_off(A, scale_a, W, scale_w, peer_out, 0, row_rank, row_pos,
+                                       m_total, m_valid_dev, N, K, G, grouped_layout, status_dev,
+                                       (cudaStream_t)stream);
+}
+
+int moeb::fp8_gemm_nt_scatter_off(const void* A, const float* scale_a, const void* W,
+                                  const float* scale_w, const uint64_t* peer_out, size_t home_off,
+                                  const int32_t* row_rank, const int32_t* row_pos, int m_total,
+                                  const int32_t* m_valid_dev, int N, int K, int G,
+                                  const int32_t* grouped_layout, int32_t* status_dev,
+                                  cudaStream_t stream) {
   if (!peer_out || !row_rank || !row_pos) {
     set_last_error_msg("moeb_fp8_grouped_gemm_nt_scatter: null scatter argument");
     return kInvalidArgument;
@@ -1309,9 +1418,10 @@ extern "C" int moeb_fp8_grouped_gemm_nt_scatter(const void* A, const float* scal
   p.G = G;
   p.m_valid = m_valid_dev;
   p.scatter_out = peer_out;
+  p.scatter_off = home_off;
   p.scatter_rank = row_rank;
   p.scatter_pos = row_pos;
-  return launch_grouped_gemm<false>(A, W, W, p, (cudaStream_t)stream);
+  return launch_grouped_gemm<false>(A, W, W, p, stream);
 }
 
 extern "C" int moeb_bf16_gemm(const void* A, const void* B, void* D, int out_dtype, int m_total,

@@ -1,11 +1,18 @@
 """Expert-parallel dispatch / combine: one process per GPU, experts split in
 contiguous blocks (owner(e) = e // (E/W), a2a_dispatch_send_tk.cuh:251).
 
-Two transports, same rows in the same canonical order, bit-identical results:
+Three transports, same rows in the same canonical order, bit-identical results:
 
-`All2All` (the reference-compatible class) — three exchanges per layer (the
-reference moves the same data with peer loads/stores into symmetric buffers
-plus a host round trip for the counts, csrc/all2all/all2all_tk.hpp:201-394):
+`EPContext` / `All2All` — the expert-parallel context of the C ABI (moeb_ep_*):
+tokens are quantised once into symmetric memory, every expert copy is announced
+to its owner with one word, the owners load the rows over NVLink (inside the
+gate/up GEMM in the fused form), results go home inside the down GEMM. One
+library call per op, no host round trip. `All2All` is the reference's class
+interface on top of it.
+
+`All2AllStaged` — three exchanges per layer (the reference moves the same data
+with peer loads/stores into symmetric buffers plus a host round trip for the
+counts, csrc/all2all/all2all_tk.hpp:201-394):
   1. counts   — all-gather of the int32[E] per-expert send counts,
   2. dispatch — all-to-all-v of packed rows (H e4m3 bytes + H/128 fp32 scales),
                 ordered by (destination rank, expert, token, slot),
@@ -66,11 +73,14 @@ def exchange_rows(send_buf: torch.Tensor, send_splits, recv_splits, group=None) 
     return recv.view(dtype)
 
 
-# ------------------------------------------------------------------ All2All --
-class All2All:
-    """Drop-in for the reference's `moe_cuda.All2All` (csrc/python_api.cpp:85-166,
-    477-514): same constructor keywords, `dispatch` / `combine` signatures and
-    properties. Differences, all forced by the transport: ranks come from
+# ------------------------------------------------------------ All2AllStaged --
+class All2AllStaged:
+    """The reference's `moe_cuda.All2All` interface (csrc/python_api.cpp:85-166,
+    477-514) over the STAGED transport: pack -> NCCL all-to-all-v -> unpack, with
+    one host read of the counts. Kept as the second, independent transport that
+    the peer-memory forms are compared with bit for bit (`All2All` below is the
+    class the operator module exports). Same constructor keywords, `dispatch` /
+    `combine` signatures and properties. Ranks come from
     torch.distributed (`group`, default world) instead of TKParallelTensor
     brokers; `max_private_tokens` is accepted and unused (no private/overflow
     split is needed); dp_group_size must be 1 (the reference's dp>1 path is
@@ -273,7 +283,7 @@ class All2All:
 
 
 # ------------------------------------------------------------- EP MoE layer --
-def ep_moe_forward(a2a: All2All, x, w_router, router_bias, gate, gate_scale, up, up_scale, down,
+def ep_moe_forward(a2a: "All2AllStaged", x, w_router, router_bias, gate, gate_scale, up, up_scale, down,
                    down_scale, out, shape, events=None):
     """Whole layer on W ranks: router -> fused quantise+pack -> dispatch ->
     gate/up SwiGLU GEMM -> down GEMM -> combine (src/moe_ops.cu:153-191 with the
@@ -315,8 +325,8 @@ def ep_moe_forward(a2a: All2All, x, w_router, router_bias, gate, gate_scale, up,
 def build_ep_step(mc, shape, d, bias_d, dev, rank, world):
     """Benchmark step for N > 1 ranks (used by bench.py)."""
     T, H, I, E, k = shape.T, shape.H, shape.I, shape.E, shape.k
-    a2a = All2All(T, E, k, 128, H, in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16,
-                  device=dev.index)
+    a2a = All2AllStaged(T, E, k, 128, H, in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16,
+                        device=dev.index)
     out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
     events = {"swiglu": [], "down": []}
 
@@ -661,3 +671,276 @@ def build_ep_step_p2p(mc, shape, d, bias_d, dev, rank, world, push_combine=True,
              "overflow": lambda: int(a2a.overflow.item()), "remote_copies": remote_copies,
              "dispatch_rows": dispatch_rows}
     return step, events, layer
+
+
+# ------------------------------------------- the C-ABI context (pull transport) --
+class EPContext:
+    """The expert-parallel context of the C ABI (moeb_ep_*; csrc/ep_ctx.cu) over
+    torch's symmetric memory: dispatch, combine, the two fused ops and the whole
+    layer are single library calls; nothing is sequenced from Python.
+
+    Transport: every rank quantises its tokens once into its symmetric buffer,
+    announces each expert copy to the owner with one 8-byte word, and the owners
+    load the rows over NVLink — in a kernel of their own (`fused=False`) or by a few
+    comm CTAs inside the gate/up GEMM while its other CTAs compute on the row
+    blocks that have landed (`fused=True`, the reference's kernel5_1 scheme).
+
+    With world size 1 (or without an initialised process group) the rank is its
+    own and only peer and a plain device buffer serves as symmetric memory."""
+
+    def __init__(self, max_num_tokens, num_experts, experts_per_token, hidden_dim,
+                 expert_padding=128, capacity_rows=None, device=None, group=None):
+        import ctypes
+        from . import moe_cuda as mc
+        self._mc = mc
+        self._ctypes = ctypes
+        if dist.is_available() and dist.is_initialized():
+            self.group = group if group is not None else dist.group.WORLD
+            self._rank = dist.get_rank(self.group)
+            self._world = dist.get_world_size(self.group)
+        else:
+            self.group, self._rank, self._world = None, 0, 1
+        self._device = torch.device("cuda", torch.cuda.current_device() if device is None
+                                    else int(device))
+        dev = self._device
+        self.T, self.E, self.k, self.H = int(max_num_tokens), int(num_experts), \
+            int(experts_per_token), int(hidden_dim)
+        self.cfg = cabi.EpConfig(self.T, self.H, self.E, self.k, int(expert_padding), self._world,
+                                 self._rank, int(capacity_rows or 0))
+        lib = cabi.load()
+        sym_bytes = lib.moeb_ep_symmetric_bytes(ctypes.byref(self.cfg))
+        loc_bytes = lib.moeb_ep_local_bytes(ctypes.byref(self.cfg))
+        if sym_bytes == 0 or loc_bytes == 0:
+            raise ValueError("bad expert-parallel configuration (hidden % 128, num_experts % world, "
+                             "top_k <= 32, expert_padding % 128)")
+        if self._world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.sym = symm_mem.empty(sym_bytes, dtype=torch.uint8, device=dev)
+            self._handle = symm_mem.rendezvous(self.sym, self.group)
+            ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        else:
+            self.sym = torch.empty(sym_bytes, dtype=torch.uint8, device=dev)
+            ptrs = [self.sym.data_ptr()]
+        self.local = torch.empty(loc_bytes, dtype=torch.uint8, device=dev)
+        peers = (ctypes.c_uint64 * self._world)(*ptrs)
+        self._ctx = ctypes.c_void_p()
+        cabi.call("moeb_ep_create", ctypes.byref(self.cfg), peers, self.local.data_ptr(), loc_bytes,
+                  self._stream(), ctypes.byref(self._ctx))
+        # nobody dispatches before every rank has cleared its flag words
+        torch.cuda.synchronize(dev)
+        if self._world > 1:
+            dist.barrier(group=self.group)
+        v = cabi.EpView()
+        cabi.call("moeb_ep_get_view", self._ctx, ctypes.byref(v))
+        self.m_cap = v.max_recv_rows
+        self.e_local = v.local_experts
+        n_kb = self.H // 128
+        loc = lambda ptr, n, dt: self._slice(self.local, ptr, n, dt)  # noqa: E731
+        self.expert_x = loc(v.expert_x, self.m_cap * self.H, torch.uint8).view(
+            self.m_cap, self.H).view(torch.float8_e4m3fn)
+        self.scale_mn = loc(v.expert_x_scale, n_kb * self.m_cap, torch.float32).view(n_kb, self.m_cap)
+        self.grouped_layout = loc(v.grouped_layout, self.m_cap, torch.int32)
+        self.m_valid = loc(v.m_valid, 1, torch.int32)
+        self.tokens_per_expert = loc(v.tokens_per_expert, self.e_local, torch.int32)
+        self.padded_offsets = loc(v.padded_offsets, self.e_local + 1, torch.int32)
+        self.source_rank = loc(v.source_rank, self.m_cap, torch.int32)
+        self.source_pos = loc(v.source_pos, self.m_cap, torch.int32)
+        self.dst_rank = loc(v.dst_rank, self.T * self.k, torch.int32).view(self.T, self.k)
+        self.dst_row = loc(v.dst_row, self.T * self.k, torch.int32).view(self.T, self.k)
+        self.overflow = loc(v.overflow, 1, torch.int32)
+        self.home = self._slice(self.sym, v.home, self.T * self.k * self.H,
+                                torch.bfloat16).view(self.T * self.k, self.H)
+        self._work = {}
+        self._n_tokens = 0
+
+    @staticmethod
+    def _slice(buf, ptr, n, dtype):
+        off = int(ptr) - buf.data_ptr()
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return buf[off:off + nbytes].view(dtype)
+
+    rank = property(lambda self: self._rank)
+    world_size = property(lambda self: self._world)
+    max_recv_tokens = property(lambda self: self.m_cap)
+
+    def _stream(self):
+        return torch.cuda.current_stream().cuda_stream
+
+    def _status(self):
+        return self._mc.status_word(self._device)
+
+    def close(self):
+        if self._ctx:
+            cabi.load().moeb_ep_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+    @staticmethod
+    def _p(t):
+        return None if t is None else t.data_ptr()
+
+    def dispatch(self, x=None, indices=None, x_q=None, x_scale_mn=None, out_expert_x=None,
+                 out_expert_x_scale=None, do_send=True, do_recv=True):
+        """x bf16 [T,H] (quantised here) or x_q e4m3 [T,H] + x_scale_mn fp32 [H/128,T];
+        indices int32 [T,k]. Results: `expert_x` / `scale_mn` (or the given output
+        tensors) and the layout fields."""
+        T = 0
+        if do_send:
+            src = x if x is not None else x_q
+            T = src.shape[0]
+            if T > self.T:
+                raise RuntimeError("num_tokens exceeds max_num_tokens")  # a2a_context_tk.hpp:150-152
+            self._n_tokens = T
+        rows = out_expert_x.shape[0] if out_expert_x is not None else 0
+        cabi.call("moeb_ep_dispatch", self._ctx, self._p(x), self._p(x_q), self._p(x_scale_mn),
+                  self._p(indices), T, self._p(out_expert_x), self._p(out_expert_x_scale), rows,
+                  int(bool(do_send)), int(bool(do_recv)), self._status()[8:].data_ptr(),
+                  self._stream())
+
+    def combine(self, out_tokens, weights, expert_y=None, accumulate=False, do_send=True,
+                do_recv=True):
+        cabi.call("moeb_ep_combine", self._ctx, self._p(expert_y), self._p(weights),
+                  self._p(out_tokens), int(bool(accumulate)), int(bool(do_send)),
+                  int(bool(do_recv)), self._status()[8:].data_ptr(), self._stream())
+
+    def fused_dispatch_swiglu(self, x, indices, gate, gate_scale, up, up_scale, D, scale_d,
+                              fused=True, x_q=None, x_scale_mn=None, out_expert_x=None,
+                              out_expert_x_scale=None):
+        src = x if x is not None else x_q
+        T = src.shape[0]
+        self._n_tokens = T
+        rows = out_expert_x.shape[0] if out_expert_x is not None else 0
+        I = gate.shape[1]
+        cabi.call("moeb_ep_fused_dispatch_swiglu", self._ctx, self._p(x), self._p(x_q),
+                  self._p(x_scale_mn), self._p(indices), T, self._p(out_expert_x),
+                  self._p(out_expert_x_scale), rows, gate.data_ptr(), gate_scale.data_ptr(),
+                  up.data_ptr(), up_scale.data_ptr(), D.data_ptr(), scale_d.data_ptr(), I,
+                  int(bool(fused)), self._status().data_ptr(), self._stream())
+
+    def fused_gemm_combine(self, A, scale_a, down, down_scale, weights, out_tokens,
+                           accumulate=False):
+        I = down.shape[2]
+        cabi.call("moeb_ep_fused_gemm_combine", self._ctx, A.data_ptr(), scale_a.data_ptr(),
+                  down.data_ptr(), down_scale.data_ptr(), I, self._p(weights), self._p(out_tokens),
+                  int(bool(accumulate)), self._status()[4:].data_ptr(), self._stream())
+
+    def moe_forward(self, x, w_router, router_bias, gate, gate_scale, up, up_scale, down,
+                    down_scale, out, shape, fused=True, indices_out=None, weights_out=None):
+        """The whole EP layer in one library call (moeb_ep_moe_forward)."""
+        ctypes = self._ctypes
+        T = x.shape[0]
+        I = gate.shape[1]
+        ws = self._work.get(I)
+        if ws is None:
+            n = cabi.load().moeb_ep_moe_forward_workspace_bytes(self._ctx, I)
+            ws = self._work[I] = torch.empty(n, dtype=torch.uint8, device=self._device)
+        cfg = cabi.LayerConfig(T, self.H, I, self.E, self.k, int(shape.router_mode),
+                               int(shape.n_group), int(shape.topk_group), int(bool(shape.renorm)),
+                               float(shape.route_scale))
+        self._n_tokens = T
+        cabi.call("moeb_ep_moe_forward", self._ctx, ctypes.byref(cfg), self._p(x), w_router.data_ptr(),
+                  self._p(router_bias), gate.data_ptr(), gate_scale.data_ptr(), up.data_ptr(),
+                  up_scale.data_ptr(), down.data_ptr(), down_scale.data_ptr(), self._p(out),
+                  self._p(indices_out), self._p(weights_out), ws.data_ptr(), ws.numel(),
+                  int(bool(fused)), self._status().data_ptr(), self._stream())
+
+    def set_timing(self, on=True):
+        cabi.call("moeb_ep_set_timing", self._ctx, int(bool(on)))
+
+    def read_timing(self):
+        """Mean stage times in ms of the recorded moe_forward calls (synchronises):
+        dict(router, dispatch_send, swiglu, down, combine, steps)."""
+        ctypes = self._ctypes
+        torch.cuda.synchronize(self._device)
+        ms = (ctypes.c_float * 5)()
+        n = ctypes.c_int(0)
+        cabi.call("moeb_ep_read_timing", self._ctx, ms, ctypes.byref(n))
+        names = ("router", "dispatch_send", "swiglu", "down", "combine")
+        out = {k: float(v) for k, v in zip(names, ms)}
+        out["steps"] = n.value
+        return out
+
+
+class All2All:
+    """Drop-in for the reference's `moe_cuda.All2All` (csrc/python_api.cpp:85-166,
+    477-514) on the C-ABI context: same constructor keywords, `dispatch` /
+    `combine` signatures (both halves, `do_send` / `do_recv`, as in
+    csrc/all2all/all2all_tk.hpp:292-334, 376-394) and properties. Ranks come from
+    torch.distributed (`group`, default world) instead of TKParallelTensor
+    brokers; `max_private_tokens` is accepted and unused (no private / overflow
+    split exists here); dp_group_size must be 1 (the reference's dp > 1 path is
+    untested, README.md:49). One op in flight per handle, like the reference.
+
+    After `dispatch`, `grouped_layout` (expert id per row, -1 padding) is what the
+    MGroupedContiguous GEMMs take."""
+
+    def __init__(self, max_num_tokens, num_experts, experts_per_token, expert_padding, hidden_dim,
+                 hidden_dim_scale=None, in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16,
+                 scale_dtype=None, max_private_tokens=None, dp_group_size=None,
+                 node_group_size=None, ep_group_size=None, device=-1, stream=None, group=None):
+        if dist.is_available() and dist.is_initialized():
+            world = dist.get_world_size(group)
+        else:
+            world = 1
+        if node_group_size is not None and int(node_group_size) != world:
+            raise ValueError("node_group_size must equal the process group size")
+        if dp_group_size not in (None, 1):
+            raise ValueError("dp_group_size must divide world size; only 1 is supported")
+        if ep_group_size is not None and (ep_group_size == 0 or world % ep_group_size != 0):
+            raise ValueError("ep_group_size must divide world size")
+        if num_experts % world != 0:
+            raise ValueError("num_experts must be a multiple of the world size")
+        if out_dtype != torch.bfloat16:
+            raise ValueError("combine only supports bfloat16")  # a2a_context_tk.hpp:181-182
+        if hidden_dim % 128 != 0:
+            raise ValueError("hidden_dim must be a multiple of 128")
+        self.ctx = EPContext(max_num_tokens, num_experts, experts_per_token, hidden_dim,
+                             expert_padding, device=None if device in (-1, None) else int(device),
+                             group=group)
+        self.k = int(experts_per_token)
+
+    rank = property(lambda self: self.ctx.rank)
+    world_size = property(lambda self: self.ctx.world_size)
+    device = property(lambda self: self.ctx._device.index)
+    max_recv_tokens = property(lambda self: self.ctx.max_recv_tokens)
+    handle = property(lambda self: self)
+    grouped_layout = property(lambda self: self.ctx.grouped_layout)
+    padded_offsets = property(lambda self: self.ctx.padded_offsets)
+    tokens_per_expert = property(lambda self: self.ctx.tokens_per_expert)
+
+    def dispatch(self, out_expert_num_tokens, out_expert_x, out_expert_x_scale=None, dp_x=None,
+                 dp_x_scale=None, indices=None, weights=None, bound_m=None, do_send=True,
+                 do_recv=True):
+        """python_api.cpp:134-143. dp_x: e4m3 [T,H]; dp_x_scale: fp32 [H/128,T]
+        (MN-major); outputs: out_expert_x e4m3 [max_recv_tokens,H],
+        out_expert_x_scale fp32 [H/128,max_recv_tokens], out_expert_num_tokens
+        uint32/int32 [E_local] = unpadded rows per local expert."""
+        if do_send:
+            if dp_x_scale is None or out_expert_x_scale is None:
+                raise ValueError("dp_x_scale and out_expert_x_scale are required")  # all2all_tk.hpp:298,327
+            if indices is None or indices.dtype != torch.int32 or indices.shape[1] != self.k:
+                raise ValueError("indices must be int32 [T, experts_per_token]")
+            if out_expert_x.shape[0] != self.max_recv_tokens or \
+                    out_expert_x_scale.shape[-1] != self.max_recv_tokens:
+                raise ValueError("out_expert_x needs max_recv_tokens rows and a [H/128, rows] scale")
+        self.ctx.dispatch(indices=indices, x_q=dp_x, x_scale_mn=dp_x_scale,
+                          out_expert_x=out_expert_x if do_send else None,
+                          out_expert_x_scale=out_expert_x_scale if do_send else None,
+                          do_send=do_send, do_recv=do_recv)
+        if do_send and out_expert_num_tokens is not None:
+            out_expert_num_tokens.view(torch.int32).copy_(self.ctx.tokens_per_expert)
+
+    def combine(self, out_tokens, indices, weights, expert_y, bound_m=None, do_send=True,
+                do_recv=True, accumulate=False):
+        """python_api.cpp:145-150: return every expert-output row to its source
+        rank and reduce out[t] = sum_j weights[t,j] * y[t,j] (bf16 in/out). Uses
+        the routing of the preceding dispatch, like the reference."""
+        if expert_y is not None and expert_y.dtype != torch.bfloat16:
+            raise ValueError("combine only supports bfloat16")
+        self.ctx.combine(out_tokens, weights, expert_y=expert_y, accumulate=accumulate,
+                         do_send=do_send, do_recv=do_recv)

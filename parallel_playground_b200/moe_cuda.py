@@ -43,6 +43,14 @@ ROUTER_SIGMOID_GROUPED = cabi.ROUTER_SIGMOID_GROUPED
 _status_words: dict[int, torch.Tensor] = {}
 
 
+def __getattr__(name):
+    # `All2All` lives in ep.py (which imports this module): resolved on first use
+    if name in ("All2All", "EPContext"):
+        from . import ep
+        return getattr(ep, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
 def init(library_root: str = "", cuda_home: str = "") -> None:
     """python_api.cpp:184-190. The reference sets JIT paths here; this build is
     compiled ahead of time, so the call only makes sure the library loads."""
@@ -490,19 +498,136 @@ class MoELayer:
         self._pipe.process(xs, outs)
 
 
-def fused_dispatch_grouped_gemm_swiglu(a2a, in_tokens, indices, gate, up, C, scale_gate, scale_up,
-                                       out_scales):
+# ------------------------------------------------- multi-GPU entry points ----
+class TKParallelTensor:
+    """Stand-in for ThunderKittens' parallel tensor as the reference's Python side
+    uses it (python/benchmark_fused_moe.py:519-535, bound in csrc/tk_bindings.cu:13-15):
+    `TKParallelTensor(shape, dtype, local_rank, local_world_size, multicast)` owns
+    one tensor per rank in peer-mapped memory, `.data()` is this rank's tensor.
+    Here it is a torch symmetric-memory allocation (a plain device tensor when the
+    process group has one rank). `multicast=True` is refused: no kernel of this
+    library reads through NVLink multicast objects."""
+
+    def __init__(self, shape, dtype, local_rank=0, local_world_size=1, multicast=False):
+        import torch.distributed as dist
+        if multicast:
+            raise ValueError("TKParallelTensor(multicast=True) is not supported: this library "
+                             "uses plain peer loads and stores only")
+        self.shape = tuple(int(v) for v in shape)
+        self.dtype = dtype
+        self.local_rank = int(local_rank)
+        self.local_world_size = int(local_world_size)
+        dev = torch.device("cuda", self.local_rank)
+        n = 1
+        for v in self.shape:
+            n *= v
+        if self.local_world_size > 1:
+            if not (dist.is_available() and dist.is_initialized()):
+                raise RuntimeError("TKParallelTensor over several ranks needs torch.distributed")
+            import torch.distributed._symmetric_memory as symm_mem
+            nbytes = max(n, 1) * torch.empty((), dtype=dtype).element_size()
+            self._raw = symm_mem.empty((nbytes + 15) // 16 * 16, dtype=torch.uint8, device=dev)
+            self._handle = symm_mem.rendezvous(self._raw, dist.group.WORLD)
+            self.raw_ptrs = [int(p) for p in self._handle.buffer_ptrs]
+            self._t = self._raw[:n * torch.empty((), dtype=dtype).element_size()].view(dtype)
+        else:
+            self._t = torch.empty(max(n, 1), dtype=dtype, device=dev)[:n]
+            self.raw_ptrs = [self._t.data_ptr()]
+        self._t = self._t.view(self.shape)
+
+    def data(self) -> torch.Tensor:
+        return self._t
+
+
+_fused_contexts: dict = {}
+
+
+def _fused_context(T, E, k, H, device):
+    """The process-wide expert-parallel context behind the reference-style fused
+    ops, whose own signatures carry no handle."""
+    from .ep import EPContext
+    key = (int(T), int(E), int(k), int(H), torch.device(device).index)
+    ctx = _fused_contexts.get(key)
+    if ctx is None:
+        ctx = _fused_contexts[key] = EPContext(T, E, k, H, device=key[4])
+    return ctx
+
+
+def _as_tensor(t):
+    return t.data() if isinstance(t, TKParallelTensor) else t
+
+
+def fused_dispatch_grouped_gemm_swiglu(*args, **kwargs):
     """csrc/tk_bindings.cu:17-60: dispatch the tokens to their experts' ranks and
-    run the gate/up SwiGLU grouped GEMM over what arrived, in one call. The
-    reference passes its ThunderKittens parallel tensors and routing maps one by
-    one; here they live in the peer-memory context `a2a` (ep.All2AllP2P).
-      in_tokens bf16 [T,H], indices int32 [T,k]; gate/up e4m3 [E_local,I,H] with
-      128x128 scales; C e4m3 [a2a.max_recv_tokens, I] and out_scales fp32
-      [I/128, a2a.max_recv_tokens] receive the re-quantised activation.
-    The two steps are stream-ordered with a rank barrier in between, not yet
-    overlapped inside one kernel. Returns the device word holding the number of
-    rows in use (a2a.m_valid)."""
+    run the gate/up SwiGLU grouped GEMM over what arrives, as one op.
+
+    Reference form (31 arguments, same order and keywords): in_tokens,
+    in_tokens_scales (parallel tensors: e4m3 [T,H], fp32 [H/128,T]),
+    expert_x_tokens, expert_x_tokens_scale (out: e4m3 [max_recv,H], fp32
+    [H/128,max_recv]), gate, up, C (out: e4m3 [max_recv,I]), scale_gate, scale_up,
+    out_scales (out: fp32 [I/128,max_recv]), indices, global_num_routed,
+    expert_to_token_map, expert_to_slot_map, padded_expert_counts, src_token_idx,
+    src_dev_idx, src_slot_idx, barrier, num_tokens, num_recv_tokens, dp_rank, rank,
+    dp_size, cur_dp_group, num_dp_groups, world_size, num_experts,
+    experts_per_token, num_comm_sms, num_comp_sms. The routing outputs
+    (padded_expert_counts [E/W], src_token_idx / src_dev_idx / src_slot_idx
+    [max_recv], num_recv_tokens [1]) are filled as the reference's kernel fills them;
+    global_num_routed, the two maps and barrier are scratch of the reference's
+    kernel and are left untouched: the state they stand for lives in this
+    library's expert-parallel context. max_recv must be the context's
+    max_recv_tokens (num_tokens*world*k padded per expert).
+
+    Short form: (a2a, in_tokens, indices, gate, up, C, scale_gate, scale_up,
+    out_scales) with a2a an ep.EPContext / ep.All2All (or ep.All2AllP2P) and bf16
+    in_tokens; returns the device word holding the rows in use."""
+    names31 = ("in_tokens", "in_tokens_scales", "expert_x_tokens", "expert_x_tokens_scale", "gate",
+               "up", "C", "scale_gate", "scale_up", "out_scales", "indices", "global_num_routed",
+               "expert_to_token_map", "expert_to_slot_map", "padded_expert_counts",
+               "src_token_idx", "src_dev_idx", "src_slot_idx", "barrier", "num_tokens",
+               "num_recv_tokens", "dp_rank", "rank", "dp_size", "cur_dp_group", "num_dp_groups",
+               "world_size", "num_experts", "experts_per_token", "num_comm_sms", "num_comp_sms")
+    if len(args) + len(kwargs) == len(names31) and "a2a" not in kwargs:
+        a = dict(zip(names31, args))
+        a.update(kwargs)
+        if set(a) != set(names31):
+            raise TypeError("fused_dispatch_grouped_gemm_swiglu: unexpected arguments")
+        if a["dp_size"] != 1:
+            raise ValueError("dp_size must be 1")   # the reference's dp > 1 path is untested, README.md:49
+        xq = _as_tensor(a["in_tokens"])
+        xs = _as_tensor(a["in_tokens_scales"])
+        T = int(a["num_tokens"])
+        H = xq.shape[1]
+        _need_cuda(xq, xs, a["expert_x_tokens"], a["expert_x_tokens_scale"], a["gate"], a["up"],
+                   a["C"], a["scale_gate"], a["scale_up"], a["out_scales"], a["indices"])
+        ctx = _fused_context(xq.shape[0], a["num_experts"], a["experts_per_token"], H, xq.device)
+        if ctx.world_size != int(a["world_size"]) or ctx.rank != int(a["rank"]):
+            raise ValueError("world_size / rank do not match the process group")
+        ctx.fused_dispatch_swiglu(None, a["indices"][:T], a["gate"], a["scale_gate"], a["up"],
+                                  a["scale_up"], a["C"], a["out_scales"], fused=True,
+                                  x_q=xq[:T], x_scale_mn=xs if T == xs.shape[1] else
+                                  xs[:, :T].contiguous(),
+                                  out_expert_x=a["expert_x_tokens"],
+                                  out_expert_x_scale=a["expert_x_tokens_scale"])
+        # routing outputs in the reference's terms
+        k = int(a["experts_per_token"])
+        off = ctx.padded_offsets
+        a["padded_expert_counts"].view(torch.int32)[:ctx.e_local].copy_(off[1:] - off[:-1])
+        n = min(a["src_token_idx"].numel(), ctx.m_cap)
+        pos = ctx.source_pos[:n]
+        live = (ctx.source_rank[:n] >= 0) & (pos >= 0)
+        a["src_token_idx"].view(torch.int32)[:n].copy_(torch.where(live, pos // k, -1))
+        a["src_slot_idx"].view(torch.int32)[:n].copy_(torch.where(live, pos % k, -1))
+        a["src_dev_idx"].view(torch.int32)[:n].copy_(ctx.source_rank[:n])
+        a["num_recv_tokens"].view(torch.int32)[:1].copy_(ctx.tokens_per_expert.sum().view(1))
+        return ctx.m_valid
+    a2a, in_tokens, indices, gate, up, C, scale_gate, scale_up, out_scales = args
     _need_cuda(in_tokens, indices, gate, up, C, scale_gate, scale_up, out_scales)
+    ctx = getattr(a2a, "ctx", a2a)
+    if hasattr(ctx, "fused_dispatch_swiglu"):
+        ctx.fused_dispatch_swiglu(in_tokens, indices, gate, scale_gate, up, scale_up, C, out_scales,
+                                  fused=kwargs.get("fused", True))
+        return ctx.m_valid
+    # ep.All2AllP2P: push dispatch, rank barrier, then the GEMM
     a2a.dispatch_bf16(in_tokens, indices)
     G, I, H = gate.shape
     cabi.call("moeb_fp8_grouped_gemm_swiglu_dyn", _ptr(a2a.expert_x), _ptr(a2a.scale_mn), _ptr(gate),
@@ -512,17 +637,49 @@ def fused_dispatch_grouped_gemm_swiglu(a2a, in_tokens, indices, gate, up, C, sca
     return a2a.m_valid
 
 
-def fused_grouped_gemm_combine(a2a, out_tokens, expert_y_tokens, expert_y_tokens_scale, down,
-                               scale_down, weights, accumulate=False):
+def fused_grouped_gemm_combine(*args, **kwargs):
     """csrc/tk_bindings.cu:62-94 (the reference ships only the launcher, its
-    kernel file is empty): the down projection whose epilogue stores every
+    kernel file is empty): the down projection whose store warps send every
     expert-output row straight to the rank its token came from, over NVLink, then
-    the weighted reduction of each token's k rows. `a2a` (ep.All2AllP2P) holds the
-    routing of the preceding dispatch.
-      expert_y_tokens e4m3 [a2a.max_recv_tokens, I] with scales fp32
-      [I/128, a2a.max_recv_tokens]; down e4m3 [E_local,H,I]; weights fp32 [T,k];
-      out_tokens bf16 [T,H]."""
+    the weighted reduction of each token's k rows.
+
+    Reference form (21 arguments, same order and keywords): out_tokens (parallel
+    tensor or tensor, bf16 [T,H]), expert_y_tokens (e4m3 [max_recv,I]),
+    expert_y_tokens_scale (fp32 [I/128,max_recv]), down, scale_down, C (unused
+    scratch), weights (fp32 [T,k]), padded_expert_counts, src_token_idx,
+    src_dev_idx, src_slot_idx, num_experts, experts_per_token, num_recv_tokens,
+    dp_rank, rank, dp_size, cur_dp_group, num_dp_groups, num_comm_sms,
+    num_comp_sms. It uses the routing of the preceding
+    fused_dispatch_grouped_gemm_swiglu call.
+
+    Short form: (a2a, out_tokens, expert_y_tokens, expert_y_tokens_scale, down,
+    scale_down, weights, accumulate=False)."""
+    names21 = ("out_tokens", "expert_y_tokens", "expert_y_tokens_scale", "down", "scale_down", "C",
+               "weights", "padded_expert_counts", "src_token_idx", "src_dev_idx", "src_slot_idx",
+               "num_experts", "experts_per_token", "num_recv_tokens", "dp_rank", "rank", "dp_size",
+               "cur_dp_group", "num_dp_groups", "num_comm_sms", "num_comp_sms")
+    if len(args) + len(kwargs) == len(names21) and "a2a" not in kwargs:
+        a = dict(zip(names21, args))
+        a.update(kwargs)
+        if set(a) != set(names21):
+            raise TypeError("fused_grouped_gemm_combine: unexpected arguments")
+        out = _as_tensor(a["out_tokens"])
+        _need_cuda(out, a["expert_y_tokens"], a["expert_y_tokens_scale"], a["down"],
+                   a["scale_down"], a["weights"])
+        T, H = out.shape
+        ctx = _fused_context(T, a["num_experts"], a["experts_per_token"], H, out.device)
+        n = ctx._n_tokens
+        ctx.fused_gemm_combine(a["expert_y_tokens"], a["expert_y_tokens_scale"], a["down"],
+                               a["scale_down"], a["weights"][:n], out[:n])
+        return None
+    a2a, out_tokens, expert_y_tokens, expert_y_tokens_scale, down, scale_down, weights = args[:7]
+    accumulate = args[7] if len(args) > 7 else kwargs.get("accumulate", False)
     _need_cuda(out_tokens, expert_y_tokens, expert_y_tokens_scale, down, scale_down, weights)
+    ctx = getattr(a2a, "ctx", a2a)
+    if hasattr(ctx, "fused_gemm_combine"):
+        ctx.fused_gemm_combine(expert_y_tokens, expert_y_tokens_scale, down, scale_down, weights,
+                               out_tokens, accumulate)
+        return None
     G, H, I = down.shape
     st = status_word(out_tokens.device)
     cabi.call("moeb_fp8_grouped_gemm_nt_scatter", _ptr(expert_y_tokens), _ptr(expert_y_tokens_scale),
@@ -530,3 +687,31 @@ def fused_grouped_gemm_combine(a2a, out_tokens, expert_y_tokens, expert_y_tokens
               _ptr(a2a.sym_pos), a2a.m_cap, _ptr(a2a.m_valid), H, I, G, _ptr(a2a.grouped_layout),
               st[4:].data_ptr(), _stream())
     a2a.combine_home(out_tokens, weights, accumulate)
+    return None
+
+
+def naive_moe_forward_dispatch(all2all, num_experts, experts_per_token, hidden_dim, gemm_type,
+                               input, input_scales, gate, gate_scales, up, up_scales, down,
+                               down_scales, indices, weights, out_tokens, expert_x,
+                               expert_x_scales, inter_y, inter_y_scales, expert_y) -> None:
+    """csrc/python_api.cpp:516-532 -> naive_moe_forward (src/moe_ops.cu:153-191):
+    dispatch -> gate/up SwiGLU grouped GEMM -> down grouped GEMM -> combine, on the
+    caller's buffers. input e4m3 [T,H] with input_scales fp32 [H/128,T]; expert_x
+    e4m3 [max_recv_tokens,H] + expert_x_scales [H/128,max_recv_tokens]; inter_y e4m3
+    [max_recv_tokens,I] + inter_y_scales [I/128,max_recv_tokens]; expert_y bf16
+    [max_recv_tokens,H]; out_tokens bf16 [T,H]. The grouped layout handed to the
+    GEMMs is the expert id per row (what they read, kernel3.cuh:136-139), not the
+    per-expert counts the reference passes there (src/moe_ops.cu:181-183)."""
+    gemm_type = GemmType(int(gemm_type))
+    if gemm_type != GemmType.MGroupedContiguous:
+        raise NotImplementedError("naive_moe_forward_dispatch: the dispatch delivers the contiguous "
+                                  "layout; MGroupedMasked is not built for it")
+    ctx = all2all.ctx
+    if (ctx.E, ctx.k, ctx.H) != (int(num_experts), int(experts_per_token), int(hidden_dim)):
+        raise ValueError("num_experts / experts_per_token / hidden_dim do not match the All2All")
+    all2all.dispatch(None, expert_x, expert_x_scales, input, input_scales, indices, weights)
+    fp8_grouped_gemm_swiglu(expert_x, expert_x_scales, gate, gate_scales, up, up_scales, inter_y,
+                            inter_y_scales, gemm_type, all2all.grouped_layout)
+    fp8_grouped_gemm_nt(inter_y, inter_y_scales, down, down_scales, expert_y, gemm_type,
+                        all2all.grouped_layout)
+    all2all.combine(out_tokens, indices, weights, expert_y)

@@ -41,8 +41,8 @@ def _worker(rank, world, port, q):
         import oracle
         from parallel_playground_b200 import moe_cuda as mc
         from parallel_playground_b200 import workloads as wl
-        from parallel_playground_b200.ep import All2All, All2AllP2P, ep_moe_forward, \
-            ep_moe_forward_p2p
+        from parallel_playground_b200.ep import All2AllStaged as All2All, All2AllP2P, \
+            ep_moe_forward, ep_moe_forward_p2p
 
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)

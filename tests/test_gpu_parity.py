@@ -874,7 +874,7 @@ def test_all2all_single_rank_dispatch_combine(mc, oracle_mod):
     """The reference's All2All interface (python_api.cpp:477-514) on one rank:
     dispatch of pre-quantised tokens equals the oracle's permutation, exact
     counts, and combine(dequant(dispatch(x))) == dequant(x) (test_all2all.cpp:621-670)."""
-    from parallel_playground_b200.ep import All2All
+    from parallel_playground_b200.ep import All2AllStaged as All2All
     T, H, E, k = 500, 2048, 16, 4
     g = torch.Generator().manual_seed(21)
     x = torch.randn(T, H, generator=g).bfloat16()
@@ -918,3 +918,58 @@ def test_all2all_single_rank_dispatch_combine(mc, oracle_mod):
     with pytest.raises(RuntimeError):
         a2a.dispatch_bf16(torch.zeros((513, H), dtype=torch.bfloat16, device=DEV),
                           torch.zeros((513, k), dtype=torch.int32, device=DEV))
+
+
+def test_module_all2all_reference_interface(mc, oracle_mod):
+    """`moe_cuda.All2All` (the exported class, on the C-ABI context) through the
+    reference's call forms (python_api.cpp:477-514), one rank, no process group:
+    exact counts, the oracle's permutation byte for byte, both halves of dispatch
+    and combine, and combine(dequant(dispatch(x))) == dequant(x)
+    (test_all2all.cpp:621-670)."""
+    T, H, E, k = 500, 2048, 16, 4
+    g = torch.Generator().manual_seed(22)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    idx = (torch.randn(T, E, generator=g).abs() + 1).topk(k, dim=1).indices.int()
+    w = torch.rand(T, k, generator=g)
+    w = (w / w.sum(1, keepdim=True)).float()
+    a2a = mc.All2All(max_num_tokens=512, num_experts=E, experts_per_token=k, expert_padding=128,
+                     hidden_dim=H, in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16,
+                     scale_dtype=torch.float32, device=0)
+    assert a2a.world_size == 1 and a2a.rank == 0 and a2a.handle is a2a
+    xq = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=DEV)
+    xs = torch.empty((H // 128, T), dtype=torch.float32, device=DEV)
+    mc.cast(x.to(DEV), xq, xs)
+    M = a2a.max_recv_tokens
+    ex = torch.zeros((M, H), dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    es = torch.zeros((H // 128, M), dtype=torch.float32, device=DEV)
+    counts = torch.zeros(E, dtype=torch.int32, device=DEV)
+    for halves in (False, True):
+        ex.view(torch.uint8).zero_()
+        es.zero_()
+        if halves:
+            a2a.dispatch(counts, ex, es, xq, xs, idx.to(DEV), w.to(DEV), do_recv=False)
+            a2a.dispatch(counts, ex, es, xq, xs, idx.to(DEV), w.to(DEV), do_send=False)
+        else:
+            a2a.dispatch(counts, ex, es, xq, xs, idx.to(DEV), w.to(DEV))
+        mc.check_device_status()
+        ref_plan = oracle_mod.route_plan(idx.numpy(), E, m_cap=M)
+        ref_x, ref_s = oracle_mod.permute_quant(x, ref_plan.dst_row, M)
+        assert np.array_equal(counts.cpu().numpy(), ref_plan.expert_counts)
+        live = ref_plan.grouped_layout >= 0
+        assert np.array_equal(_u8(ex)[live], ref_x[live])
+        assert np.array_equal(es.cpu().numpy()[:, live], ref_s[:, live])
+        rows = ref_plan.m_padded
+        assert np.array_equal(a2a.grouped_layout.cpu().numpy()[:rows], ref_plan.grouped_layout[:rows])
+    y = oracle_mod.dequant_rows(ref_x, ref_s).bfloat16().to(DEV)
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=DEV)
+    a2a.combine(out, idx.to(DEV), w.to(DEV), y, do_recv=False)
+    a2a.combine(out, idx.to(DEV), w.to(DEV), y, do_send=False)
+    mc.check_device_status()
+    ref_out = oracle_mod.unpermute_combine(y.cpu(), ref_plan.dst_row, w.numpy(), H)
+    assert torch.equal(out.cpu().view(torch.int16), ref_out.view(torch.int16))
+    x_deq = (xq.float().cpu().view(T, H // 128, 128) * xs.cpu().t()[:, :, None]).reshape(T, H)
+    assert torch.allclose(out.float().cpu(), x_deq, atol=3e-2, rtol=1e-2)
+    with pytest.raises(RuntimeError):
+        a2a.dispatch(counts, ex, es, torch.zeros((513, H), dtype=torch.float8_e4m3fn, device=DEV),
+                     torch.zeros((H // 128, 513), device=DEV),
+                     torch.zeros((513, k), dtype=torch.int32, device=DEV), None)

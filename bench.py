@@ -46,9 +46,18 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=None, help="tokens per rank (default: workload's)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=1024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ep-transport", default="p2p", choices=["p2p", "nccl"],
-                    help="N > 1: peer-memory loads/stores by this library's kernels (p2p) or "
-                         "packed rows through NCCL all-to-all (nccl)")
+    ap.add_argument("--ep-transport", default="ctx", choices=["ctx", "p2p", "nccl"],
+                    help="N > 1: the C-ABI expert-parallel context (ctx: one library call per "
+                         "layer, rows pulled over NVLink, inside the gate/up GEMM when fused), the "
+                         "push transport sequenced from Python (p2p), or packed rows through NCCL "
+                         "all-to-all (nccl)")
+    ap.add_argument("--ep-fused", type=int, default=1, choices=[0, 1],
+                    help="ctx transport: dispatch fused into the gate/up GEMM (1) or fetched by a "
+                         "kernel of its own first (0)")
+    ap.add_argument("--no-targets", action="store_true",
+                    help="skip the short runs of the other configurations (the `targets` key)")
+    ap.add_argument("--no-parity", action="store_true",
+                    help="N > 1: skip the untimed parity leg (the `parity` key)")
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under a profiler: skip the e2e leg, the FP8 peak probe and the "
                          "CPU baseline (their keys are null)")
@@ -177,38 +186,58 @@ def nvlink_bytes(gpu_index):
 
 
 # ------------------------------------------------------------------ CPU arm --
-def cpu_reference_arm(shape, sample_tokens, steps, warmup):
+def cpu_reference_arm(shape, sample_tokens, steps, warmup, world=1):
     """Times the oracle (a CPU restatement of the reference path, fp32 on the
     de-quantised FP8 weights, torch CPU matmul on every host core) on a bounded
-    sample of the workload's tokens. Weight de-quantisation is preparation and
-    is not timed, like the GPU arm's pre-quantised weights."""
+    sample of the workload's tokens, all `shape.E` experts present. Up to 64
+    experts the weights are de-quantised beforehand (preparation, not timed, like
+    the GPU arm's pre-quantised weights); beyond that the fp32 copies would not fit
+    the host and each expert is de-quantised when its rows are processed, inside
+    the timed region."""
     import numpy as np
     import oracle
     torch.set_num_threads(os.cpu_count() or 1)
     sub = dataclasses.replace(shape, T=sample_tokens)
-    inp = wl.make_layer_inputs(sub)
-    bias = popularity_bias(shape)
-    if bias is None:
-        bias = inp.router_bias          # e.g. the Zipf bias of the Mixtral-shaped workload
+    g = torch.Generator().manual_seed(shape.seed)
+    x = torch.randn(sample_tokens, shape.H, generator=g).bfloat16()
+    gr = torch.Generator().manual_seed(1000 + shape.seed)
+    w_router = (torch.randn(shape.H, shape.E, generator=gr) * 0.02).bfloat16()
+    bias = popularity_bias(shape, world)
+    if bias is None and shape.zipf_bias > 0:
+        bias = wl.zipf_log_bias(shape.E, shape.zipf_bias)
     q = lambda t: t.view(torch.uint8).numpy()  # noqa: E731
-    gw = oracle.dequant_weight(q(inp.gate), inp.gate_scale.numpy())
-    uw = oracle.dequant_weight(q(inp.up), inp.up_scale.numpy())
-    dw = oracle.dequant_weight(q(inp.down), inp.down_scale.numpy())
+    keep_f32 = shape.E <= 64
+    experts = []
+    for e in range(shape.E):
+        w = wl.make_expert_weights(shape, e)
+        if keep_f32:
+            experts.append(tuple(oracle.dequant_weight(q(w[n]), w[n + "_scale"].numpy())[0]
+                                 for n in ("gate", "up", "down")))
+        else:
+            experts.append(w)
+
+    def weights_of(e):
+        if keep_f32:
+            return experts[e]
+        w = experts[e]
+        return tuple(oracle.dequant_weight(q(w[n]), w[n + "_scale"].numpy())[0]
+                     for n in ("gate", "up", "down"))
 
     def step():
-        logits = oracle.router_logits(inp.x, inp.w_router, bias)
+        logits = oracle.router_logits(x, w_router, bias)
         idx, w = oracle.router_select(logits, sub.k, sub.router_mode, sub.n_group, sub.topk_group,
                                       sub.renorm, sub.route_scale)
         plan = oracle.route_plan(idx, sub.E)
-        ex, es = oracle.permute_quant(inp.x, plan.dst_row, plan.m_cap)
+        ex, es = oracle.permute_quant(x, plan.dst_row, plan.m_cap)
         a = oracle.dequant_rows(ex, es)
         y = torch.zeros((plan.m_cap, sub.H))
-        for g, rows in oracle._group_rows(plan.grouped_layout, sub.E, False, 0):
+        for e, rows in oracle._group_rows(plan.grouped_layout, sub.E, False, 0):
+            gw, uw, dw = weights_of(e)
             ar = a[rows]
-            gate = ar @ gw[g].T
-            act = (ar @ uw[g].T) * gate / (1.0 + torch.exp(-gate))
+            gate = ar @ gw.T
+            act = (ar @ uw.T) * gate / (1.0 + torch.exp(-gate))
             dq, ds = oracle.quant_f32_1x128(act.numpy(), mn_major=True)
-            y[rows] = oracle.dequant_rows(dq, ds) @ dw[g].T
+            y[rows] = oracle.dequant_rows(dq, ds) @ dw.T
         return oracle.unpermute_combine(y.bfloat16(), plan.dst_row, w, sub.H)
 
     for _ in range(warmup):
@@ -220,23 +249,27 @@ def cpu_reference_arm(shape, sample_tokens, steps, warmup):
     return {"value": sample_tokens / dt, "unit": "tokens/s", "cores": torch.get_num_threads(),
             "kind": "port", "ms_per_step": dt * 1e3,
             "sample": f"{sample_tokens} tokens of the workload through all {sub.E} experts, "
-                      f"{steps} timed passes, weights pre-dequantised (not timed)"}
+                      f"{steps} timed passes, weights " +
+                      ("pre-dequantised (not timed)" if keep_f32 else
+                       "de-quantised per expert inside the timed pass")}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    shape = bench_shape(args, 1)
-    steps = max(1, min(args.steps, 3))
-    warm = 1 if args.warmup > 0 else 0
-    cb = cpu_reference_arm(shape, args.cpu_sample_tokens, steps, warm)
+    world = max(1, args.gpus)
+    shape = bench_shape(args, world)
+    steps = max(1, min(args.steps, 3 if world == 1 else 1))
+    warm = 1 if (args.warmup > 0 and world == 1) else 0
+    cb = cpu_reference_arm(shape, args.cpu_sample_tokens, steps, warm, world)
     line = {
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": cb["value"],
         "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
         "ms_per_step": cb["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 (CPU, de-quantised e4m3 inputs)", "data": "synthetic",
-        "config": workload_config(shape, 1),
+        "config": workload_config(shape, world, args.ep_transport, args.ep_combine, args.ep_dispatch,
+                                  args.ep_fused),
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
@@ -246,7 +279,7 @@ def run_reference(args):
     return 0
 
 
-def workload_config(shape, world, transport=None, combine=None, dispatch=None):
+def workload_config(shape, world, transport=None, combine=None, dispatch=None, fused=None):
     return {"workload": f"{shape.name}: MoE layer T={shape.T}/rank H={shape.H} I={shape.I} "
                         f"E={shape.E} top-{shape.k}, e4m3 1x128/128x128 scales",
             "tokens_per_rank": shape.T, "hidden": shape.H, "intermediate": shape.I,
@@ -254,6 +287,7 @@ def workload_config(shape, world, transport=None, combine=None, dispatch=None):
             "ep_transport": transport if world > 1 else None,
             "ep_combine": combine if (world > 1 and transport == "p2p") else None,
             "ep_dispatch": dispatch if (world > 1 and transport == "p2p") else None,
+            "ep_dispatch_fused_into_gemm": bool(fused) if (world > 1 and transport == "ctx") else None,
             "expert_popularity": ("log Dirichlet(1) bias over a rank's experts, the same profile on "
                                   "every rank" if shape.name == "gemm32" else
                                   (f"log Zipf({shape.zipf_bias}) bias" if shape.zipf_bias > 0
@@ -311,6 +345,338 @@ def fp8_peak_tflops(dev, gpu_index=0, sustained_s=2.0):
         return None
 
 
+# DRAM traffic of one gate/up launch of the gemm32 shape (H=4096, I=1536, 32 local
+# experts), from an ncu capture of a 16 384-row launch: the FP8 weights are read
+# once (2*E_local*I*H bytes) and every routed row adds 5 267 bytes
+# (dram__bytes_read.sum + dram__bytes_write.sum; 489.0 MB in total for that launch).
+GEMM32_GATEUP_DRAM_BYTES_PER_ROW = 5267.0
+
+
+def setup_inputs(args, shape, world, rank, dev):
+    inp = wl.make_layer_inputs(shape, rank=rank, world=world, weights_device=str(dev))
+    d = inp.to(dev)
+    bias = popularity_bias(shape, world)
+    if bias is None:
+        bias = inp.router_bias          # e.g. the Zipf bias of the Mixtral-shaped workload
+    bias_d = None if bias is None else bias.to(dev)
+    return inp, d, bias_d
+
+
+def build_step(mc, args, shape, d, bias_d, dev, rank, world, fused=None):
+    if world == 1:
+        return build_single_gpu_step(mc, shape, d, bias_d, dev)
+    if args.ep_transport == "ctx":
+        return build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world,
+                                 bool(args.ep_fused) if fused is None else fused)
+    from parallel_playground_b200.ep import build_ep_step, build_ep_step_p2p
+    if args.ep_transport == "p2p":
+        return build_ep_step_p2p(mc, shape, d, bias_d, dev, rank, world,
+                                 push_combine=args.ep_combine == "push",
+                                 once_per_rank=args.ep_dispatch == "once")
+    return build_ep_step(mc, shape, d, bias_d, dev, rank, world)
+
+
+def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused):
+    """N > 1 ranks through the C-ABI expert-parallel context: the whole layer is
+    one library call per step; stage times come from CUDA events that the library
+    records around its launches."""
+    from parallel_playground_b200.ep import EPContext
+    T, H = shape.T, shape.H
+    ctx = EPContext(T, shape.E, shape.k, H, device=dev.index)
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    idx = torch.empty((T, shape.k), dtype=torch.int32, device=dev)
+    wts = torch.empty((T, shape.k), dtype=torch.float32, device=dev)
+    state = {"timing": False}
+
+    def run(x_dev, out_dev, want_routing=False):
+        ctx.moe_forward(x_dev, d.w_router, bias_d, d.gate, d.gate_scale, d.up, d.up_scale, d.down,
+                        d.down_scale, out_dev, shape, fused=fused,
+                        indices_out=idx if want_routing else None,
+                        weights_out=wts if want_routing else None)
+
+    def step(timed: bool):
+        if timed and not state["timing"]:
+            ctx.set_timing(True)
+            state["timing"] = True
+        run(d.x, out)
+
+    def stage_ms():
+        tm = ctx.read_timing()
+        ctx.set_timing(False)
+        state["timing"] = False
+        return tm
+
+    def remote_copies():
+        valid = ctx.dst_rank >= 0
+        return int((valid & (ctx.dst_rank != rank)).sum().item())
+
+    # cast, plan x3, exchange+plan, mark, announce, [pull,] gate/up GEMM, pos, down GEMM,
+    # barrier, reduce + router x2
+    layer = {"kernels_per_step": 14 if fused else 15, "out": out, "ctx": ctx, "run": run,
+             "routed_rows": lambda: int(ctx.tokens_per_expert.sum().item()),
+             "e2e_fn": lambda x_dev, out_dev: run(x_dev, out_dev),
+             "overflow": lambda: int(ctx.overflow.item()), "remote_copies": remote_copies,
+             "dispatch_rows": remote_copies, "stage_ms": stage_ms, "idx": idx, "wts": wts,
+             "fused": fused}
+    return step, None, layer
+
+
+def timed_steps(mc, step, steps, warmup, dev, world, rank, local_rank, sample_clocks):
+    """W untimed steps, then exactly K steps between barrier + synchronize on both
+    sides, CUDA events on the launching stream, max over ranks."""
+    import torch.distributed as dist
+    for _ in range(max(warmup, 3)):
+        step(False)
+    torch.cuda.synchronize()
+    mc.check_device_status()
+    sampler = ClockSampler(local_rank) if sample_clocks else None
+    if sampler is not None and rank == 0:
+        sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step(True)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if (sampler is not None and rank == 0) else None
+    mc.check_device_status()
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    return ms_total / steps, clocks
+
+
+def collect_stages(stage_events, layer):
+    """Mean stage times in ms of the timed steps: from the library's own events
+    (ctx transport) or from the events recorded around the Python-issued launches."""
+    if "stage_ms" in layer:
+        tm = layer["stage_ms"]()
+        return {"swiglu": tm["swiglu"], "down": tm["down"], "dispatch": tm["dispatch_send"],
+                "dispatch_recv": tm["dispatch_recv"], "combine": tm["combine"],
+                "router": tm["router"], "steps_recorded": tm["steps"]}
+    out = {}
+    for name in ("swiglu", "down", "dispatch", "combine", "dispatch_kernel"):
+        if stage_events.get(name):
+            out[name] = statistics.mean(a.elapsed_time(b) for a, b in stage_events[name])
+    return out
+
+
+def gemm_figures(shape, world, rows, st, peaks, fp8):
+    """TFLOP/s of the two grouped GEMMs and their roofline records. The launches
+    are timed one by one with CUDA events inside a timed region of well under two
+    seconds, so the denominator is the BURST rate of cuBLASLt's e4m3 GEMM measured
+    in this run; the sustained rate and the nominal peak are printed beside it."""
+    H, I = shape.H, shape.I
+    e_local = shape.E // world
+    burst = fp8["burst"] if fp8 else 2.0 * peaks["bf16_tflops"]
+    burst_src = ("cuBLASLt e4m3 8192^3, best of 10 in this run (burst)" if fp8 else
+                 f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']})")
+    sustained = fp8["sustained"] if fp8 and fp8.get("sustained") else None
+
+    def record(kernel, flops, ms, alg_bytes):
+        ach = flops / (ms * 1e-3) / 1e12
+        r = {"bound": "tensor", "kernel": kernel, "achieved": ach, "peak": burst,
+             "unit": "TFLOP/s", "frac": ach / burst, "peak_source": burst_src,
+             "peak_sustained": sustained,
+             "frac_of_sustained": ach / sustained if sustained else None,
+             "peak_bf16_x2": 2.0 * peaks["bf16_tflops"], "peak_nominal": 4500.0,
+             "frac_of_nominal": ach / 4500.0, "flops_per_launch": flops, "ms_per_launch": ms,
+             "algorithmic_bytes": alg_bytes, "traffic": None}
+        # few rows per expert (decode sizes): reading the FP8 weights takes longer than
+        # the contraction, so the launch is judged against the measured HBM bandwidth
+        t_tensor = flops / (burst * 1e12)
+        t_hbm = alg_bytes / (peaks["hbm_gbs"] * 1e9)
+        if t_hbm > t_tensor:
+            gbs = alg_bytes / (ms * 1e-3) / 1e9
+            r.update({"bound": "hbm", "achieved_tensor": ach, "frac_tensor": ach / burst,
+                      "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                      "frac": gbs / peaks["hbm_gbs"],
+                      "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})"})
+        return r
+
+    up = record("grouped_gemm_fp8_kernel<swiglu> (gate/up + SwiGLU + requant)",
+                4.0 * rows * H * I, st["swiglu"],
+                2.0 * e_local * I * H + rows * (H + 4.0 * (H // 128) + I + 4.0 * (I // 128)))
+    dn = record("grouped_gemm_fp8_kernel<down> (down projection, bf16 rows out)",
+                2.0 * rows * H * I, st["down"],
+                1.0 * e_local * I * H + rows * (I + 4.0 * (I // 128) + 2.0 * H))
+    if shape.name == "gemm32":
+        up["traffic"] = 2.0 * e_local * I * H + GEMM32_GATEUP_DRAM_BYTES_PER_ROW * rows
+        up["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of a 16 384-row "
+                                "launch of this shape: weights once + 5 267 B per routed row, "
+                                "scaled to this launch's rows")
+    return up, dn
+
+
+def transport_figures(shape, world, layer, st, args):
+    """NVLink figures of the EP transport (rank 0's view): algorithmic bytes over
+    CUDA-event times, against 900 GB/s per direction."""
+    H = shape.H
+    row_b = wl.dispatch_row_bytes(H)
+    remote = layer["remote_copies"]()
+    sent = layer["dispatch_rows"]() if "dispatch_rows" in layer else remote
+    out = {"remote_copies": remote, "dispatch_rows_moved": sent, "overflow_copies": layer["overflow"](),
+           "nvlink_peak_gbs_per_direction": 900.0, "dispatch_ms": st.get("dispatch"),
+           "combine_ms": st.get("combine")}
+    if args.ep_transport == "ctx":
+        fused = layer["fused"]
+        # the rows cross NVLink in the receive half: inside the gate/up GEMM (fused) or
+        # in the pull kernel; the results go home inside the down GEMM
+        xfer_ms = st["swiglu"] if fused else st["dispatch_recv"]
+        out.update({"dispatch_fused_into_gemm": bool(fused),
+                    "dispatch_recv_ms": st["dispatch_recv"],
+                    "dispatch_transfer_in": "swiglu_gemm" if fused else "pull kernel",
+                    "dispatch_nvlink_gbs": sent * row_b / (xfer_ms * 1e-3) / 1e9,
+                    "dispatch_nvlink_frac": sent * row_b / (xfer_ms * 1e-3) / 1e9 / 900.0,
+                    "dispatch_phase_ms": st["dispatch"] + st["dispatch_recv"],
+                    "combine_transfer_in": "down_gemm",
+                    "combine_nvlink_gbs": remote * 2.0 * H / (st["down"] * 1e-3) / 1e9,
+                    "combine_nvlink_frac": remote * 2.0 * H / (st["down"] * 1e-3) / 1e9 / 900.0})
+        return out
+    push = args.ep_transport == "p2p" and args.ep_combine == "push"
+    xfer_ms = st["down"] if push else st["combine"]
+    if "dispatch_kernel" in st:
+        out["dispatch_kernel_ms"] = st["dispatch_kernel"]
+        out["dispatch_kernel_nvlink_gbs"] = sent * row_b / (st["dispatch_kernel"] * 1e-3) / 1e9
+    out.update({"dispatch_nvlink_gbs": sent * row_b / (st["dispatch"] * 1e-3) / 1e9,
+                "combine_nvlink_gbs": remote * 2.0 * H / (xfer_ms * 1e-3) / 1e9,
+                "combine_transfer_in": "down_gemm" if push else "combine"})
+    return out
+
+
+def parity_leg(mc, args, shape, inp, d, bias_d, dev, rank, world, layer):
+    """N > 1, outside the timed region. Every rank checks, for its own tokens:
+      * routing: the layer's indices and weights equal the CPU oracle's selection
+        on the same logits, bit for bit;
+      * expert outputs: for eight experts, one owned by each rank (so rows travel
+        both ways over every pair of ranks), every (token, slot) copy of the first
+        256 tokens routed to them is recomputed by the oracle from the same FP8
+        inputs (fp32 on de-quantised operands, intermediate re-quantised 1x128) and
+        compared with the row that came home: max|err|/max|ref| <= 2e-2, mean|err|
+        <= 1e-3;
+      * the whole output equals, bit for bit, the output of the staged transport
+        (pack -> NCCL all-to-all-v -> unpack), an independent second path.
+    The verdict is all-reduced; the oracle is the checker here, never the timed path."""
+    import numpy as np
+    import torch.distributed as dist
+    import oracle
+    from parallel_playground_b200.ep import All2AllStaged, ep_moe_forward
+    T, H, I, E, k = shape.T, shape.H, shape.I, shape.E, shape.k
+    ctx = layer["ctx"]
+    out = layer["out"]
+    layer["run"](d.x, out, True)
+    torch.cuda.synchronize()
+    idx, wts = layer["idx"], layer["wts"]
+    n_chk = min(T, 256)
+    logits = torch.empty((T, E), dtype=torch.float32, device=dev)
+    mc.router_logits(d.x, d.w_router, logits, bias_d)
+    ref_idx, ref_w = oracle.router_select(logits[:n_chk].cpu().numpy(), k, shape.router_mode,
+                                          shape.n_group, shape.topk_group, shape.renorm,
+                                          shape.route_scale)
+    routing_exact = bool(np.array_equal(idx[:n_chk].cpu().numpy(), ref_idx) and
+                         np.array_equal(wts[:n_chk].cpu().numpy().view(np.uint32),
+                                        ref_w.view(np.uint32)))
+    e_local = E // world
+    chosen = [r * e_local + (rank + r) % e_local for r in range(world)]
+    # the checked experts' weights are regenerated with the seeds of their owners
+    home = ctx.home.view(ctx.T, k, H)
+    xq, xs = oracle.cast_1x128(inp.x[:n_chk], mn_major=True)
+    max_rel = mean_abs = 0.0
+    pairs = 0
+    q = lambda t: t.view(torch.uint8).cpu().numpy()  # noqa: E731
+    for e in chosen:
+        sel = (idx[:n_chk] == e).nonzero()
+        if sel.numel() == 0:
+            continue
+        toks, slots = sel[:, 0].cpu().numpy(), sel[:, 1].cpu().numpy()
+        w = wl.make_expert_weights(shape, e, weights_device=str(dev))
+        lay = np.zeros(toks.size, np.int32)
+        a_q = np.ascontiguousarray(xq[toks])
+        a_s = np.ascontiguousarray(xs[:, toks])
+        _, d_ref, sd_ref = oracle.grouped_gemm_swiglu_ref(a_q, a_s, q(w["gate"]),
+                                                          w["gate_scale"].cpu().numpy(),
+                                                          q(w["up"]), w["up_scale"].cpu().numpy(), lay)
+        y_ref = oracle.grouped_gemm_ref(d_ref, sd_ref, q(w["down"]), w["down_scale"].cpu().numpy(), lay)
+        got = home[torch.from_numpy(toks).to(dev), torch.from_numpy(slots).to(dev)].float().cpu().numpy()
+        err = np.abs(got - y_ref)
+        max_rel = max(max_rel, float(err.max() / max(np.abs(y_ref).max(), 1e-30)))
+        mean_abs = max(mean_abs, float(err.mean()))
+        pairs += int(toks.size)
+    # second transport, whole batch
+    staged = All2AllStaged(T, E, k, 128, H, in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16,
+                           device=dev.index)
+    out2 = torch.empty_like(out)
+    ep_moe_forward(staged, d.x, d.w_router, bias_d, d.gate, d.gate_scale, d.up, d.up_scale, d.down,
+                   d.down_scale, out2, shape)
+    torch.cuda.synchronize()
+    same = bool(torch.equal(out.view(torch.int16), out2.view(torch.int16)))
+    del staged, out2
+    ok = routing_exact and same and max_rel <= 2e-2 and mean_abs <= 1e-3 and pairs > 0
+    t = torch.tensor([0.0 if ok else 1.0, 0.0 if routing_exact else 1.0, 0.0 if same else 1.0,
+                      max_rel, mean_abs, float(pairs)], device=dev)
+    worst = t.clone()
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    total = t[5:6].clone()
+    dist.all_reduce(total)
+    return {"ok": bool(worst[0].item() == 0.0), "routing_exact": bool(worst[1].item() == 0.0),
+            "matches_staged_transport": bool(worst[2].item() == 0.0),
+            "max_rel": float(worst[3].item()), "mean_abs": float(worst[4].item()),
+            "sampled_pairs": int(total.item()), "ranks": world,
+            "tolerance": "routing bit-exact; rows max|err|/max|ref| <= 2e-2, mean|err| <= 1e-3 "
+                         "against the CPU oracle on the same FP8 inputs; output bit-identical to the "
+                         "staged NCCL transport"}
+
+
+TARGET_WORKLOADS = {1: ["qwen3", "mixtral", "dsv3_decode"], 2: ["qwen3"], 4: ["qwen3"],
+                    8: ["dsv3_prefill", "dsv3_decode", "mixtral", "qwen3"]}
+
+
+def run_target(mc, args, name, world, rank, local_rank, dev, peaks, fp8):
+    """A short run (8 timed steps) of another benchmark configuration at this N:
+    ms/step, tokens/s, both GEMMs against their rooflines and, for N > 1, the
+    NVLink figures of the dispatch (fused into the GEMM, and fetched by the pull
+    kernel alone) and of the combine."""
+    import gc
+    shape = wl.CONFIGS[name]
+    inp, d, bias_d = setup_inputs(args, shape, world, rank, dev)
+    res = {"workload": workload_config(shape, world, args.ep_transport)["workload"]}
+    modes = [None] if (world == 1 or args.ep_transport != "ctx") else [True, False]
+    for fused in modes:
+        step, ev, layer = build_step(mc, args, shape, d, bias_d, dev, rank, world, fused)
+        ms_step, _ = timed_steps(mc, step, 8, 3, dev, world, rank, local_rank, False)
+        st = collect_stages(ev, layer)
+        rows = int(layer["routed_rows"]())
+        if rank == 0:
+            up, dn = gemm_figures(shape, world, rows, st, peaks, fp8)
+            rec = {"ms_per_step": ms_step, "tokens_per_s": shape.T * world / (ms_step * 1e-3),
+                   "routed_rows": rows, "gate_up": {k_: up[k_] for k_ in
+                                                    ("bound", "achieved", "unit", "frac", "peak",
+                                                     "ms_per_launch", "frac_of_nominal")},
+                   "down": {k_: dn[k_] for k_ in ("bound", "achieved", "unit", "frac", "peak",
+                                                  "ms_per_launch", "frac_of_nominal")},
+                   "layer_tflops": 6.0 * rows * shape.H * shape.I / (ms_step * 1e-3) / 1e12}
+            if world > 1:
+                rec["transport"] = transport_figures(shape, world, layer, st, args)
+            key = "result" if fused is None else ("fused" if fused else "unfused")
+            res[key] = rec
+        if "ctx" in layer:
+            layer["ctx"].close()
+        del step, ev, layer
+        gc.collect()
+        torch.cuda.empty_cache()
+    del inp, d, bias_d
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_b200(args):
     import torch.distributed as dist
     from parallel_playground_b200 import moe_cuda as mc
@@ -327,167 +693,90 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=dev)
 
     shape = bench_shape(args, world)
-    inp = wl.make_layer_inputs(shape, rank=rank, world=world, weights_device=str(dev))
-    d = inp.to(dev)
-    bias = popularity_bias(shape, world)
-    if bias is None:
-        bias = inp.router_bias          # e.g. the Zipf bias of the Mixtral-shaped workload
-    bias_d = None if bias is None else bias.to(dev)
+    inp, d, bias_d = setup_inputs(args, shape, world, rank, dev)
     T, H, I, E, k = shape.T, shape.H, shape.I, shape.E, shape.k
-    E_local = E // world
+    step, stage_events, layer = build_step(mc, args, shape, d, bias_d, dev, rank, world)
 
-    if world == 1:
-        step, stage_events, layer = build_single_gpu_step(mc, shape, d, bias_d, dev)
-    else:
-        from parallel_playground_b200.ep import build_ep_step, build_ep_step_p2p
-        builder = build_ep_step_p2p if args.ep_transport == "p2p" else build_ep_step
-        kw = {"push_combine": args.ep_combine == "push",
-              "once_per_rank": args.ep_dispatch == "once"} if args.ep_transport == "p2p" else {}
-        step, stage_events, layer = builder(mc, shape, d, bias_d, dev, rank, world, **kw)
-
-    for _ in range(max(args.warmup, 3)):
-        step(False)
-    torch.cuda.synchronize()
-    mc.check_device_status()
-
-    sampler = ClockSampler(local_rank)
     nvl0 = nvlink_bytes(local_rank) if (rank == 0 and world > 1) else None
-    if rank == 0:
-        sampler.start()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step(True)
-    e1.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    ms_total = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    ms_step, clocks = timed_steps(mc, step, args.steps, args.warmup, dev, world, rank, local_rank,
+                                  True)
     nvl1 = nvlink_bytes(local_rank) if nvl0 is not None else None
-    mc.check_device_status()
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
     tokens_per_s = T * world / (ms_step * 1e-3)
-
-    # dominant kernel: gate/up grouped GEMM, timed inside the timed region
-    gemm_ms = [a.elapsed_time(b) for a, b in stage_events["swiglu"]]
-    down_ms = [a.elapsed_time(b) for a, b in stage_events["down"]]
+    st = collect_stages(stage_events, layer)
     rows = int(layer["routed_rows"]())
-    swiglu_ms = statistics.mean(gemm_ms)
-    swiglu_tflops = 4.0 * rows * H * I / (swiglu_ms * 1e-3) / 1e12
-    down_tflops = 2.0 * rows * H * I / (statistics.mean(down_ms) * 1e-3) / 1e12
 
-    # e2e through the public host-buffer call (rank-local; N=1 only uses the C-ABI single call)
+    # e2e through the public host-buffer call (rank-local; N=1 uses the C-ABI single call)
     e2e = None if args.profile_mode else measure_e2e(mc, layer, shape, inp, dev, world, args)
+    parity = None
+    if world > 1 and args.ep_transport == "ctx" and not args.no_parity and not args.profile_mode:
+        parity = parity_leg(mc, args, shape, inp, d, bias_d, dev, rank, world, layer)
+    transport = transport_figures(shape, world, layer, st, args) \
+        if (world > 1 and "remote_copies" in layer) else None
+
+    peaks = measured_peaks()
+    fp8 = None
+    if rank == 0 and not args.profile_mode:
+        fp8 = fp8_peak_tflops(dev, local_rank)
+    targets = None
+    if not args.no_targets and not args.profile_mode and args.workload == "gemm32" \
+            and not args.tokens:
+        if "ctx" in layer:
+            layer["ctx"].close()
+        del step, stage_events, d, bias_d
+        layer = {"kernels_per_step": layer["kernels_per_step"]}
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        targets = [run_target(mc, args, name, world, rank, local_rank, dev, peaks, fp8)
+                   for name in TARGET_WORKLOADS.get(world, [])]
 
     if rank != 0:
         if world > 1:
+            dist.barrier()
             dist.destroy_process_group()
-        return 0
-    peaks = measured_peaks()
-    # The GEMM is timed inside a long step loop, under the power cap: the
-    # denominator is the sustained cuBLASLt FP8 rate; the burst rate is printed beside it.
-    fp8 = None if args.profile_mode else fp8_peak_tflops(dev, local_rank)
-    if fp8 and fp8["sustained"]:
-        peak, peak_source = fp8["sustained"], "cuBLASLt e4m3 8192^3, back to back for 2 s in this run (sustained)"
-    elif fp8:
-        peak, peak_source = fp8["burst"], "cuBLASLt e4m3 8192^3, best of 10 in this run (burst)"
-    else:
-        peak = 2.0 * peaks["bf16_tflops_sustained"]
-        peak_source = f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})"
-    burst = fp8["burst"] if fp8 else 2.0 * peaks["bf16_tflops"]
-    # DRAM traffic of the gate/up launch, from the ncu capture of a small case of
-    # this shape (profiles/grouped_gemm_fp8__gemm32_small.md: 16 384 rows, 489.0 MB):
-    # the FP8 weights are read once (402.7 MB), the rest grows with the rows.
-    traffic = traffic_source = None
-    if shape.name == "gemm32":
-        per_row = (489.0e6 - 402.7e6) / 16384.0
-        traffic = 2.0 * E_local * I * H + per_row * rows
-        traffic_source = ("ncu dram__bytes_read+write of a 16 384-row launch of this shape, weights "
-                          "once + 5 267 B per routed row, scaled to this launch's rows")
+        return 0 if (parity is None or parity["ok"]) else 1
+    up, dn = gemm_figures(shape, world, rows, st, peaks, fp8)
     line = {
         "metric": "moe_layer_tokens_per_s", "value": tokens_per_s, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "e4m3 x e4m3 -> f32 (bf16 in/out)", "data": "synthetic",
-        "config": workload_config(shape, world, args.ep_transport, args.ep_combine, args.ep_dispatch),
+        "config": workload_config(shape, world, args.ep_transport, args.ep_combine, args.ep_dispatch,
+                                  args.ep_fused),
         "clocks": clocks,
         "e2e": e2e,
         "gpu_launches": layer["kernels_per_step"] * args.steps,
-        "roofline": {
-            "bound": "tensor", "kernel": "grouped_gemm_fp8_kernel<swiglu> (gate/up + SwiGLU + requant)",
-            "achieved": swiglu_tflops, "peak": peak, "unit": "TFLOP/s", "frac": swiglu_tflops / peak,
-            "peak_source": peak_source,
-            "peak_sm_mhz": fp8["sustained_sm_mhz"] if fp8 else None,
-            "peak_burst": burst, "frac_of_burst": swiglu_tflops / burst,
-            "peak_bf16_x2": 2.0 * peaks["bf16_tflops"], "peak_nominal": 4500.0,
-            "flops_per_launch": 4.0 * rows * H * I, "ms_per_launch": swiglu_ms,
-            "traffic": traffic, "traffic_source": traffic_source,
-            "algorithmic_bytes": 2.0 * E_local * I * H + rows * (H + 4.0 * (H // 128) + I + 4.0 * (I // 128)),
-        },
-        "stages": {"swiglu_gemm_ms": swiglu_ms, "down_gemm_ms": statistics.mean(down_ms),
-                   "down_gemm_tflops": down_tflops, "routed_rows": rows,
+        "roofline": up,
+        "roofline_down": dn,
+        "stages": {"swiglu_gemm_ms": st["swiglu"], "down_gemm_ms": st["down"],
+                   "down_gemm_tflops": 2.0 * rows * H * I / (st["down"] * 1e-3) / 1e12,
+                   "routed_rows": rows,
                    "layer_tflops": 6.0 * rows * H * I / (ms_step * 1e-3) / 1e12},
     }
-    # Few rows per expert (decode sizes): reading the FP8 weights takes longer than
-    # the contraction, so the same launch is judged against the measured HBM copy
-    # bandwidth instead (the tensor figures stay in the line as *_tensor keys).
-    rl = line["roofline"]
-    t_tensor = rl["flops_per_launch"] / (peak * 1e12)
-    t_hbm = rl["algorithmic_bytes"] / (peaks["hbm_gbs"] * 1e9)
-    if t_hbm > t_tensor:
-        achieved_gbs = rl["algorithmic_bytes"] / (swiglu_ms * 1e-3) / 1e9
-        rl.update({"bound": "hbm", "achieved_tensor": rl["achieved"], "frac_tensor": rl["frac"],
-                   "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                   "frac": achieved_gbs / peaks["hbm_gbs"],
-                   "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})"})
-    if world > 1 and "dispatch" in stage_events:
-        # transport phases of the peer-memory path (rank 0's view): plan + count
-        # exchange + quantise/peer-store + fence, and fence + peer-load reduce
-        disp_ms = statistics.mean(a.elapsed_time(b) for a, b in stage_events["dispatch"])
-        comb_ms = statistics.mean(a.elapsed_time(b) for a, b in stage_events["combine"])
-        remote = layer["remote_copies"]()
-        sent = layer["dispatch_rows"]() if "dispatch_rows" in layer else remote
-        row_b = wl.dispatch_row_bytes(H)
-        # push combine: the rows travel inside the down GEMM's epilogue and the
-        # "combine" phase is only the local weighted reduction
-        push = args.ep_transport == "p2p" and args.ep_combine == "push"
-        xfer_ms = statistics.mean(down_ms) if push else comb_ms
-        if stage_events.get("dispatch_kernel"):
-            # the quantise + peer-store kernel alone (the phase above also holds the
-            # plan, the count exchange and the fence that waits for the slowest rank)
-            dk_ms = statistics.mean(a.elapsed_time(b) for a, b in stage_events["dispatch_kernel"])
-            line["stages"].update({"dispatch_kernel_ms": dk_ms,
-                                   "dispatch_kernel_nvlink_gbs": sent * row_b / (dk_ms * 1e-3) / 1e9})
-        line["stages"].update({
-            "dispatch_ms": disp_ms, "combine_ms": comb_ms, "remote_copies": remote,
-            "dispatch_rows_sent": sent,
-            "dispatch_nvlink_gbs": sent * row_b / (disp_ms * 1e-3) / 1e9,
-            "combine_nvlink_gbs": remote * 2 * H / (xfer_ms * 1e-3) / 1e9,
-            "combine_transfer_in": "down_gemm" if push else "combine",
-            "nvlink_peak_gbs_per_direction": 900.0,
+    if transport is not None:
+        transport.update({
             # the hardware's own NVLink data counters over the timed steps (rank 0's GPU),
-            # beside the algorithmic bytes: dispatch rows out + result rows out per step
+            # beside the algorithmic bytes: rows in + result rows out per step
             "nvlink_counter_tx_bytes_per_step": ((nvl1[0] - nvl0[0]) / args.steps
                                                  if nvl0 and nvl1 else None),
             "nvlink_counter_rx_bytes_per_step": ((nvl1[1] - nvl0[1]) / args.steps
-                                                 if nvl0 and nvl1 else None),
-            "nvlink_algorithmic_tx_bytes_per_step": sent * row_b + remote * 2.0 * H,
-            "overflow_copies": layer["overflow"]()})
+                                                 if nvl0 and nvl1 else None)})
+        line["stages"].update(transport)
+    if parity is not None:
+        line["parity"] = parity
+    if targets is not None:
+        line["targets"] = targets
+        line["targets_note"] = ("short runs (8 timed steps) of the other benchmark configurations at "
+                                "this N; north-star bars at the DeepSeek-V3 shape, EP=8: grouped GEMMs "
+                                ">= 0.60 of FP8 peak, dispatch/combine >= 0.70 of 900 GB/s per direction")
     if not args.no_cpu_baseline and not args.profile_mode and world == 1:
         cb = cpu_reference_arm(shape, args.cpu_sample_tokens, 2, 1)
         line["cpu_baseline"] = {k_: cb[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
-    return 0
+    return 0 if (parity is None or parity["ok"]) else 1
 
 
 def build_single_gpu_step(mc, shape, d, bias_d, dev):

@@ -488,10 +488,10 @@ int moeb_ep_moe_forward(moeb_ep_ctx *ctx, const moeb_layer_config *cfg, const vo
  * reference brackets its launches with NVTX ranges, csrc/runtime/utils.h:7-15): after
  * moeb_ep_set_timing(ctx, 1) up to 64 calls are recorded; moeb_ep_read_timing (after the
  * stream has been synchronised) returns the mean milliseconds of {router, dispatch send
- * half, gate/up GEMM incl. the receive half, down GEMM, barrier + reduction} and the number
- * of calls, and starts a new series. */
+ * half, dispatch receive half (0 when it is fused into the GEMM), gate/up GEMM, down GEMM,
+ * barrier + reduction} and the number of calls, and starts a new series. */
 int moeb_ep_set_timing(moeb_ep_ctx *ctx, int enable);
-int moeb_ep_read_timing(moeb_ep_ctx *ctx, float *stage_ms5, int *steps);
+int moeb_ep_read_timing(moeb_ep_ctx *ctx, float *stage_ms6, int *steps);
 
 #ifdef __cplusplus
 }

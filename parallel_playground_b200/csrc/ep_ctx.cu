@@ -34,7 +34,7 @@ namespace moeb {
 constexpr int kEpCtxMaxWorld = 64;
 constexpr int kEpCtxMaxExperts = 1024;
 constexpr int kTimingSlots = 64;   // steps whose stage events are kept
-constexpr int kTimingStages = 6;   // start, router, dispatch-send, gate/up, down, combine
+constexpr int kTimingStages = 7;   // start, router, dispatch send, dispatch receive, gate/up, down, combine
 
 static size_t al256(size_t x) { return (x + 255) / 256 * 256; }
 
@@ -769,6 +769,7 @@ extern "C" int moeb_ep_fused_dispatch_swiglu(moeb_ep_ctx* c, const void* x_bf16,
   const int32_t* layout = at<const int32_t>(L, c->loc.grouped_layout);
   const int32_t* m_valid = at<const int32_t>(L, c->loc.m_valid);
   if (fused) {
+    record_stage(c, 3, s);   // (the receive half runs inside the GEMM)
     const PullParams q = make_pull(c, status_dev);
     if ((rc = fp8_swiglu_fused_dispatch(c->out_x, c->out_scale, gate_q, gate_scale, up_q, up_scale,
                                         D, scale_d, c->out_rows, m_valid, intermediate,
@@ -780,6 +781,7 @@ extern "C" int moeb_ep_fused_dispatch_swiglu(moeb_ep_ctx* c, const void* x_bf16,
     c->received = true;
   } else {
     if ((rc = dispatch_recv(c, status_dev, s))) return rc;
+    record_stage(c, 3, s);
     if ((rc = moeb_fp8_grouped_gemm_swiglu_dyn(c->out_x, c->out_scale, gate_q, gate_scale, up_q,
                                                up_scale, D, scale_d, c->out_rows, m_valid,
                                                intermediate, c->cfg.hidden, c->e_local,
@@ -787,7 +789,7 @@ extern "C" int moeb_ep_fused_dispatch_swiglu(moeb_ep_ctx* c, const void* x_bf16,
                                                status_dev, s)))
       return rc;
   }
-  record_stage(c, 3, s);
+  record_stage(c, 4, s);
   return kOk;
 }
 
@@ -812,7 +814,7 @@ extern "C" int moeb_ep_fused_gemm_combine(moeb_ep_ctx* c, const void* A, const f
                                     intermediate, c->e_local,
                                     at<const int32_t>(L, c->loc.grouped_layout), status_dev, s)))
     return rc;
-  record_stage(c, 4, s);
+  record_stage(c, 5, s);
   return combine_recv(c, weights, out_bf16, accumulate, status_dev ? status_dev + 4 : nullptr, s);
 }
 
@@ -876,7 +878,7 @@ extern "C" int moeb_ep_moe_forward(moeb_ep_ctx* c, const moeb_layer_config* cfg,
   if ((rc = moeb_ep_fused_gemm_combine(c, inter, inter_scale, down_q, down_scale, cfg->I, weights,
                                        out_bf16, 0, status_dev ? status_dev + 4 : nullptr, stream)))
     return rc;
-  record_stage(c, 5, s);
+  record_stage(c, 6, s);
   if (c->timing && c->timing_n < kTimingSlots) c->timing_n += 1;
   if (indices_out && T > 0)
     MOEB_CUDA_TRY(cudaMemcpyAsync(indices_out, indices, (size_t)T * g.top_k * 4,

@@ -93,6 +93,7 @@ struct GemmParams {
   int m_total, N, K, G;
   int masked, max_m, out_f32;
   int num_m_blocks, num_n_blocks;
+  int group_m;             // row blocks walked together (tile order), see tile_mn
   const int32_t* m_valid;  // optional device word: rows in use (<= m_total); blocks beyond it are not visited
   // optional scatter epilogue of the down projection (EP combine fused into the
   // GEMM): row r is stored to peer buffer scatter_out[scatter_rank[r]] at row
@@ -116,17 +117,37 @@ struct TileInfo {
   bool valid;
 };
 
+// Tile index -> (row block, N block). group_m <= 1: N fastest, so the CTAs of a
+// wave share few row blocks and cover every N block of them. With many N blocks
+// (wide experts) a wave would then touch every weight tile of an expert once and
+// never again before it has left L2; group_m > 1 walks group_m row blocks together,
+// row block fastest, so that a wave re-uses each weight tile group_m times.
+__device__ __forceinline__ void tile_mn(const GemmParams& p, int tile, int& m_block, int& n_block) {
+  if (p.group_m <= 1) {
+    m_block = tile / p.num_n_blocks;
+    n_block = tile - m_block * p.num_n_blocks;
+    return;
+  }
+  const int per_group = p.group_m * p.num_n_blocks;
+  const int grp = tile / per_group;
+  const int w = tile - grp * per_group;
+  const int m0 = grp * p.group_m;
+  const int gm = min(p.group_m, p.num_m_blocks - m0);
+  n_block = w / gm;
+  m_block = m0 + (w - n_block * gm);
+}
+
 // The one layout word that decides a tile: the expert id of the block's first
 // row (contiguous) or the expert's row count (masked).
 __device__ __forceinline__ size_t tile_key_index(const GemmParams& p, int tile) {
-  const int m_block = tile / p.num_n_blocks;
+  int m_block, n_block;
+  tile_mn(p, tile, m_block, n_block);
   return p.masked ? (size_t)(m_block / (p.max_m / kBM)) : (size_t)m_block * kBM;
 }
 
 __device__ __forceinline__ TileInfo make_tile(const GemmParams& p, int tile, int key) {
   TileInfo t;
-  t.m_block = tile / p.num_n_blocks;
-  t.n_block = tile - t.m_block * p.num_n_blocks;
+  tile_mn(p, tile, t.m_block, t.n_block);
   if (!p.masked) {
     // every expert's rows start on a multiple of 128, so the first row decides
     t.g = key;
@@ -147,8 +168,7 @@ __device__ __forceinline__ TileInfo make_tile(const GemmParams& p, int tile, int
 // critical path of every K block).
 __device__ __forceinline__ TileInfo get_tile(const GemmParams& p, int tile) {
   TileInfo t;
-  t.m_block = tile / p.num_n_blocks;
-  t.n_block = tile - t.m_block * p.num_n_blocks;
+  tile_mn(p, tile, t.m_block, t.n_block);
   if (!p.masked) {
     t.g = __ldg(p.layout + (size_t)t.m_block * kBM);
     t.valid = t.g >= 0 && t.g < p.G;
@@ -351,7 +371,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
   // with a device-side row count (EP: known only after the count exchange) the
   // tile range shrinks to the rows in use
   int num_m_blocks = p.num_m_blocks;
-  if (p.m_valid != nullptr) num_m_blocks = min(num_m_blocks, ceil_div(max(__ldg(p.m_valid), 0), kBM));
+  if (p.m_valid != nullptr) {
+    num_m_blocks = min(num_m_blocks, ceil_div(max(__ldg(p.m_valid), 0), kBM));
+    // whole groups of row blocks (blocks past the rows in use hold padding only)
+    if (p.group_m > 1) num_m_blocks = min(p.num_m_blocks, round_up(num_m_blocks, p.group_m));
+  }
   const int num_tiles = num_m_blocks * p.num_n_blocks;
   const int num_kb = p.K / kBK;
   // tiles are dealt round-robin to the CTAs that run the GEMM
@@ -1187,6 +1211,22 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
   p.wait_hint_ns = gemm_wait_hint_ns();
   p.num_m_blocks = ceil_div(p.m_total, kBM);
   p.num_n_blocks = kSwiglu ? p.N / 128 : ceil_div(p.N, 256);
+  // Tactic: tile order by the number of N blocks (the reference picks block sizes
+  // by waves and last-wave use, csrc/jit_kernels/heuristics/heuristics.hpp:136-281;
+  // here the tile is fixed at 128 x 256 and the walk is what the shapes differ in).
+  // CUDA-event sweep on B200, one launch each, gate/up | down in ms:
+  //   N blocks (shape)            group_m = 1      4        8        16
+  //   112 | 16 (H4096 I14336)     4.86 | 2.20  4.51|2.12  4.35|2.10  4.27|2.10
+  //    16 | 28 (H7168 I2048)      0.989| 0.548 .979|.519  .972|.521  .974|.532
+  //    12 | 16 (H4096 I1536)      0.834| 0.464 .841|.452  .841|.460  .839|.447
+  //     6 |  8 (H2048 I768)       0.243| 0.177 .242|.177  .242|.177  .242|.177
+  // MOEB_GEMM_GROUP_M overrides the choice (sweeps).
+  static const int group_env = [] {
+    const char* e = getenv("MOEB_GEMM_GROUP_M");
+    return e ? atoi(e) : 0;
+  }();
+  p.group_m = group_env > 0 ? group_env : (p.num_n_blocks >= 32 ? 16 : p.num_n_blocks >= 14 ? 8 : 1);
+  if (p.masked) p.group_m = 1;
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const GemmParams);
   // Measured on B200 (one launch each, default workload): gate/up with the tanh

@@ -854,13 +854,13 @@ class EPContext:
 
     def read_timing(self):
         """Mean stage times in ms of the recorded moe_forward calls (synchronises):
-        dict(router, dispatch_send, swiglu, down, combine, steps)."""
+        dict(router, dispatch_send, dispatch_recv, swiglu, down, combine, steps)."""
         ctypes = self._ctypes
         torch.cuda.synchronize(self._device)
-        ms = (ctypes.c_float * 5)()
+        ms = (ctypes.c_float * 6)()
         n = ctypes.c_int(0)
         cabi.call("moeb_ep_read_timing", self._ctx, ms, ctypes.byref(n))
-        names = ("router", "dispatch_send", "swiglu", "down", "combine")
+        names = ("router", "dispatch_send", "dispatch_recv", "swiglu", "down", "combine")
         out = {k: float(v) for k, v in zip(names, ms)}
         out["steps"] = n.value
         return out

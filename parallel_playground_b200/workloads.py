@@ -109,10 +109,7 @@ def make_layer_inputs(shape: LayerShape, rank: int = 0, world: int = 1, T: int |
     def expert_weights(tag: int, n: int, k: int):
         qs, ss = [], []
         for e in range(rank * E_local, (rank + 1) * E_local):
-            ge = torch.Generator(device=weights_device).manual_seed(
-                (shape.seed * 7919 + tag) * 100003 + e)
-            w = torch.randn(1, n, k, generator=ge, device=weights_device) * 0.02
-            q, s = quantize_weights_128x128(w.bfloat16())
+            q, s = _one_expert_matrix(shape, tag, e, n, k, weights_device)
             qs.append(q)
             ss.append(s)
         return torch.cat(qs), torch.cat(ss)
@@ -121,6 +118,25 @@ def make_layer_inputs(shape: LayerShape, rank: int = 0, world: int = 1, T: int |
     up, up_s = expert_weights(2, shape.I, shape.H)
     down, down_s = expert_weights(3, shape.H, shape.I)
     return LayerInputs(shape, x, w_router, bias, gate, gate_s, up, up_s, down, down_s)
+
+
+def _one_expert_matrix(shape: LayerShape, tag: int, e: int, n: int, k: int, weights_device: str):
+    """One weight matrix [1,n,k] of GLOBAL expert e, N(0, 0.02), quantised. The
+    seed depends on the expert id only, so every EP split sees the same expert;
+    the random stream depends on the device kind (CPU and CUDA generators differ)."""
+    ge = torch.Generator(device=weights_device).manual_seed((shape.seed * 7919 + tag) * 100003 + e)
+    w = torch.randn(1, n, k, generator=ge, device=weights_device) * 0.02
+    return quantize_weights_128x128(w.bfloat16())
+
+
+def make_expert_weights(shape: LayerShape, e: int, weights_device: str = "cpu") -> dict:
+    """The three quantised matrices of global expert e, bit-identical to what
+    make_layer_inputs(..., weights_device=same kind of device) gives its owner."""
+    gate, gate_s = _one_expert_matrix(shape, 1, e, shape.I, shape.H, weights_device)
+    up, up_s = _one_expert_matrix(shape, 2, e, shape.I, shape.H, weights_device)
+    down, down_s = _one_expert_matrix(shape, 3, e, shape.H, shape.I, weights_device)
+    return {"gate": gate, "gate_scale": gate_s, "up": up, "up_scale": up_s, "down": down,
+            "down_scale": down_s}
 
 
 def dirichlet_multinomial_indices(T: int, E: int, k: int, seed: int, alpha: float = 1.0):

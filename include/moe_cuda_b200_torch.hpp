@@ -9,18 +9,26 @@
 // throws std::runtime_error where the reference prints and exits
 // (moe_cuda/include/moe_cuda/error.hpp:11-22).
 //
+// Expert parallel: All2AllBase / make_all2all / naive_moe_forward_dispatch
+// (csrc/all2all/all2all_base.hpp:11-52) over the C-ABI context moeb_ep_*; the
+// caller hands make_all2all the peer-mapped symmetric buffers, which the
+// reference obtains from ThunderKittens' TKParallelTensor.
+//
 // Not provided: GemmType::Batched, and the at::Tensor forms of
-// fused_dispatch_grouped_gemm_swiglu / fused_grouped_gemm_combine (their
-// TKParallelTensor arguments, internal_api.hpp:63-85, have no counterpart here;
-// the Python module offers both over its peer-memory context).
+// fused_dispatch_grouped_gemm_swiglu / fused_grouped_gemm_combine with
+// TKParallelTensor arguments (internal_api.hpp:63-85): moeb_ep_fused_dispatch_swiglu
+// / moeb_ep_fused_gemm_combine take the context instead, and the Python module
+// offers the reference's 31- / 21-argument forms.
 #pragma once
 
 #include <cuda_runtime_api.h>
 #include <torch/types.h>
 
+#include <memory>
 #include <optional>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "moe_cuda_b200.h"
 
@@ -255,6 +263,174 @@ inline void moe_forward(const moeb_layer_config &cfg, at::Tensor &x, at::Tensor 
                        out.data_ptr(), nullptr, nullptr, workspace.data_ptr(),
                        (size_t)workspace.numel(), nullptr, stream),
       "moe_forward");
+}
+
+// ---- expert parallel ---------------------------------------------------------
+// csrc/runtime/parallel.h:3-9
+struct ParallelConfig {
+  uint32_t tp_size;
+  uint32_t dp_size;
+  uint32_t ep_size;
+  uint32_t node_size;
+  uint32_t world_size;
+};
+
+// csrc/all2all/all2all_base.hpp:11-31
+class All2AllBase {
+ public:
+  All2AllBase() = default;
+  virtual ~All2AllBase() = default;
+  virtual void dispatch(at::Tensor &out_expert_num_tokens, at::Tensor &out_expert_x,
+                        std::optional<at::Tensor> &out_expert_x_scale, at::Tensor &dp_x,
+                        std::optional<at::Tensor> &dp_x_scale, at::Tensor &indices,
+                        at::Tensor &weights, std::optional<at::Tensor> &bound_m,
+                        bool do_send = true, bool do_recv = true,
+                        cudaStream_t stream = nullptr) = 0;
+  virtual void combine(at::Tensor &out_tokens, at::Tensor &indices, at::Tensor &weights,
+                       at::Tensor &expert_y, std::optional<at::Tensor> &bound_m,
+                       bool do_send = true, bool do_recv = true, bool accumulate = false,
+                       cudaStream_t stream = nullptr) = 0;
+  virtual uint32_t max_recv_tokens() const = 0;
+  // per-row expert id (-1 padding) of the rows the last dispatch delivered: the
+  // grouped layout of the MGroupedContiguous GEMMs
+  virtual int *grouped_layout() const = 0;
+};
+
+// All2AllBase over the C-ABI context. The symmetric buffers (one per rank, each
+// moeb_ep_symmetric_bytes(cfg) bytes, mapped into this process) and the local
+// workspace are the caller's; `local_workspace` is kept alive by this object.
+class All2AllContext final : public All2AllBase {
+ public:
+  All2AllContext(const moeb_ep_config &cfg, const std::vector<uint64_t> &peer_base,
+                 at::Tensor local_workspace, cudaStream_t stream)
+      : cfg_(cfg), local_(std::move(local_workspace)) {
+    detail::need((int)peer_base.size() == cfg.world, "one symmetric buffer address per rank");
+    detail::check(moeb_ep_create(&cfg_, peer_base.data(), local_.data_ptr(),
+                                 (size_t)local_.numel() * local_.element_size(), stream, &ctx_),
+                  "All2All");
+    detail::check(moeb_ep_get_view(ctx_, &view_), "All2All");
+  }
+  ~All2AllContext() override { moeb_ep_destroy(ctx_); }
+  All2AllContext(const All2AllContext &) = delete;
+  All2AllContext &operator=(const All2AllContext &) = delete;
+
+  void dispatch(at::Tensor &out_expert_num_tokens, at::Tensor &out_expert_x,
+                std::optional<at::Tensor> &out_expert_x_scale, at::Tensor &dp_x,
+                std::optional<at::Tensor> &dp_x_scale, at::Tensor &indices, at::Tensor &weights,
+                std::optional<at::Tensor> &bound_m, bool do_send = true, bool do_recv = true,
+                cudaStream_t stream = nullptr) override {
+    (void)weights;
+    (void)bound_m;   // validated and unused by the reference as well (all2all_tk.hpp:284-290)
+    if (do_send) {
+      // all2all_tk.hpp:298,327: both scale tensors are dereferenced unconditionally
+      detail::need(dp_x_scale.has_value() && out_expert_x_scale.has_value(),
+                   "dp_x_scale and out_expert_x_scale are required");
+      detail::need(indices.scalar_type() == at::kInt, "indices must be int32 [T, k]");
+    }
+    detail::check(
+        moeb_ep_dispatch(ctx_, nullptr, do_send ? dp_x.data_ptr() : nullptr,
+                         do_send ? dp_x_scale->data_ptr<float>() : nullptr,
+                         do_send ? indices.data_ptr<int>() : nullptr,
+                         do_send ? (int)dp_x.size(0) : 0, do_send ? out_expert_x.data_ptr() : nullptr,
+                         do_send ? out_expert_x_scale->data_ptr<float>() : nullptr,
+                         do_send ? (int)out_expert_x.size(0) : 0, do_send, do_recv, nullptr, stream),
+        "All2All::dispatch");
+    if (do_send)   // unpadded rows per local expert (all2all_tk.hpp:216-219,317-320)
+      cudaMemcpyAsync(out_expert_num_tokens.data_ptr(), view_.tokens_per_expert,
+                      sizeof(int32_t) * view_.local_experts, cudaMemcpyDeviceToDevice, stream);
+  }
+  void combine(at::Tensor &out_tokens, at::Tensor &indices, at::Tensor &weights,
+               at::Tensor &expert_y, std::optional<at::Tensor> &bound_m, bool do_send = true,
+               bool do_recv = true, bool accumulate = false,
+               cudaStream_t stream = nullptr) override {
+    (void)indices;
+    (void)bound_m;
+    detail::need(expert_y.scalar_type() == at::kBFloat16 && out_tokens.scalar_type() == at::kBFloat16,
+                 "combine only supports bfloat16");   // a2a_context_tk.hpp:181-182
+    detail::check(moeb_ep_combine(ctx_, expert_y.data_ptr(), weights.data_ptr<float>(),
+                                  out_tokens.data_ptr(), accumulate, do_send, do_recv, nullptr,
+                                  stream),
+                  "All2All::combine");
+  }
+  uint32_t max_recv_tokens() const override { return (uint32_t)view_.max_recv_rows; }
+  int *grouped_layout() const override { return view_.grouped_layout; }
+  moeb_ep_ctx *handle() const { return ctx_; }
+
+ private:
+  moeb_ep_config cfg_;
+  at::Tensor local_;
+  moeb_ep_ctx *ctx_ = nullptr;
+  moeb_ep_view view_{};
+};
+
+// csrc/all2all/all2all_base.hpp:33-41. The reference's version allocates its
+// parallel tensors itself; this one is given them: `peer_base` holds the address
+// of every rank's symmetric buffer (moeb_ep_symmetric_bytes bytes each) in this
+// process. in/out/scale dtypes are e4m3 / bf16 / fp32 (the only ones the
+// reference's transport supports, a2a_context_tk.hpp:181-195); dp_size must be 1.
+// (make_all2all_ranked: CUDA device and rank given separately; make_all2all below
+// takes local_rank for both, as the reference does.)
+inline std::shared_ptr<All2AllBase> make_all2all_ranked(
+    uint32_t max_num_tokens, uint32_t num_experts, uint32_t experts_per_token,
+    uint32_t expert_padding, uint32_t hidden_dim, std::optional<uint32_t> hidden_dim_scale,
+    c10::ScalarType in_dtype, c10::ScalarType out_dtype, std::optional<c10::ScalarType> scale_dtype,
+    std::optional<uint32_t> max_private_tokens_opt, int device, int rank,
+    ParallelConfig parallel_config, const std::vector<uint64_t> &peer_base, cudaStream_t stream) {
+  (void)hidden_dim_scale;
+  (void)max_private_tokens_opt;   // no private / overflow split in this transport
+  detail::need(in_dtype == at::kFloat8_e4m3fn && out_dtype == at::kBFloat16 &&
+                   (!scale_dtype.has_value() || *scale_dtype == at::kFloat),
+               "All2All moves e4m3 tokens with fp32 scales out and bf16 rows back");
+  detail::need(parallel_config.dp_size <= 1, "dp_size must be 1");
+  moeb_ep_config cfg{(int)max_num_tokens, (int)hidden_dim,        (int)num_experts,
+                     (int)experts_per_token, (int)expert_padding, (int)parallel_config.world_size,
+                     rank,                0};
+  const size_t bytes = moeb_ep_local_bytes(&cfg);
+  detail::need(bytes > 0, "bad expert-parallel configuration");
+  at::Tensor ws = at::empty({(int64_t)bytes},
+                            at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device));
+  return std::make_shared<All2AllContext>(cfg, peer_base, ws, stream);
+}
+
+inline std::shared_ptr<All2AllBase> make_all2all(
+    uint32_t max_num_tokens, uint32_t num_experts, uint32_t experts_per_token,
+    uint32_t expert_padding, uint32_t hidden_dim, std::optional<uint32_t> hidden_dim_scale,
+    c10::ScalarType in_dtype, c10::ScalarType out_dtype, std::optional<c10::ScalarType> scale_dtype,
+    std::optional<uint32_t> max_private_tokens_opt, int local_rank, ParallelConfig parallel_config,
+    const std::vector<uint64_t> &peer_base, cudaStream_t stream) {
+  return make_all2all_ranked(max_num_tokens, num_experts, experts_per_token, expert_padding,
+                             hidden_dim, hidden_dim_scale, in_dtype, out_dtype, scale_dtype,
+                             max_private_tokens_opt, local_rank, local_rank, parallel_config,
+                             peer_base, stream);
+}
+
+// csrc/all2all/all2all_base.hpp:43-52 -> src/moe_ops.cu:153-239: dispatch -> gate/up
+// SwiGLU grouped GEMM -> down grouped GEMM -> combine on the caller's buffers.
+// The GEMMs get the per-row expert ids of the dispatch as their layout.
+inline void naive_moe_forward_dispatch(All2AllBase &a2a, uint32_t num_experts,
+                                       uint32_t experts_per_token, uint32_t hidden_dim,
+                                       GemmType gemm_type, at::Tensor &input,
+                                       at::Tensor &input_scales, at::Tensor &gate,
+                                       at::Tensor &gate_scales, at::Tensor &up,
+                                       at::Tensor &up_scales, at::Tensor &down,
+                                       at::Tensor &down_scales, at::Tensor &indices,
+                                       at::Tensor &weights, at::Tensor &out_tokens,
+                                       at::Tensor &expert_x, at::Tensor &expert_x_scales,
+                                       at::Tensor &inter_y, at::Tensor &inter_y_scales,
+                                       at::Tensor &expert_y, cudaStream_t stream) {
+  (void)num_experts;
+  (void)experts_per_token;
+  (void)hidden_dim;
+  detail::need(gemm_type == GemmType::MGroupedContiguous,
+               "the dispatch delivers the contiguous layout");
+  at::Tensor counts = at::empty({(int64_t)gate.size(0)}, indices.options());
+  std::optional<at::Tensor> xs(expert_x_scales), is(input_scales), none;
+  a2a.dispatch(counts, expert_x, xs, input, is, indices, weights, none, true, true, stream);
+  kernels::fp8_grouped_gemm_swiglu(expert_x, gate, up, expert_x_scales, gate_scales, up_scales,
+                                   inter_y_scales, inter_y, gemm_type, a2a.grouped_layout(), stream);
+  kernels::fp8_grouped_gemm_nt(inter_y, inter_y_scales, down, down_scales, expert_y, gemm_type,
+                               a2a.grouped_layout(), stream);
+  a2a.combine(out_tokens, indices, weights, expert_y, none, true, true, false, stream);
 }
 
 }  // namespace moe_cuda

@@ -50,7 +50,8 @@ struct LocalLayout {
 };
 
 static bool ep_config_ok(const moeb_ep_config* c) {
-  return c && c->max_tokens > 0 && c->hidden > 0 && c->hidden % 128 == 0 && c->num_experts > 0 &&
+  return c && c->max_tokens > 0 && c->hidden > 0 && c->hidden % 128 == 0 && c->hidden <= 8192 &&
+         c->num_experts > 0 &&
          c->num_experts <= kEpCtxMaxExperts && c->top_k > 0 && c->top_k <= 32 &&
          c->expert_padding > 0 && c->expert_padding % 128 == 0 && c->world > 0 &&
          c->world <= kEpCtxMaxWorld && c->rank >= 0 && c->rank < c->world &&
@@ -616,8 +617,8 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
   LocalLayout ll;
   if (!ep_config_ok(cfg) || !sym_layout(*cfg, &sl) || !local_layout(*cfg, &ll)) {
     set_last_error_msg(
-        "moeb_ep_create: bad configuration (hidden % 128, num_experts % world, top_k <= 32, "
-        "expert_padding % 128, world <= 64)");
+        "moeb_ep_create: bad configuration (hidden % 128, hidden <= 8192, num_experts % world, "
+        "top_k <= 32, expert_padding % 128, world <= 64)");
     return kInvalidArgument;
   }
   if (!peer_base_host || !local_workspace || local_bytes < ll.total ||

@@ -21,8 +21,8 @@
 //      rank with 16-byte / 4-byte peer loads (plain loads, no TMA multicast),
 //   3. stores them to expert_x[r,:] and, MN-major, to scale[kb*m_cap + r],
 //   4. publishes the row: fence, then one gpu-scope add on arrived[r/128].
-// Rows of one warp are fetched two at a time so that more loads are in flight
-// over NVLink. Every wait is bounded; on expiry the status word gets
+// A warp fetches several rows per pass so that more loads are in flight over
+// NVLink. Every wait is bounded; on expiry the status word gets
 // {4, 7 (role: pull), row, tag} and the worker stops.
 #pragma once
 
@@ -106,69 +106,89 @@ __device__ __forceinline__ int pull_wait_pos(const PullParams& q, int r) {
   }
 }
 
-// `worker` of `n_workers` warps; all 32 lanes call it together.
+// One pass of a worker warp: kRows consecutive rows (all in one 128-row block),
+// each up to kVec * 512 bytes wide. Lanes 0..kRows-1 poll the rows' words at the
+// same time; every load of the pass (rows and scales, local or over NVLink) is in
+// flight before the first store; one fence and one counter update per pass.
+template <int kRows, int kVec>
+__device__ __forceinline__ bool pull_pass(const PullParams& q, int r0, int rows, int n_kb,
+                                          int vec_per_row, int lane) {
+  int my_src = -1, my_pos = -1;
+  if (lane < kRows && r0 + lane < rows) {
+    my_src = q.source_rank[r0 + lane];
+    if (my_src >= 0) {
+      my_pos = pull_wait_pos(q, r0 + lane);
+      if (my_pos < 0) my_src = -2;  // the wait ran out
+    }
+  }
+  if (__any_sync(0xffffffffu, my_src == -2)) return false;
+  const uint4* from[kRows];
+  const float* sfrom[kRows];
+  bool live[kRows];
+  int n_done = 0;
+#pragma unroll
+  for (int j = 0; j < kRows; ++j) {
+    const int src = __shfl_sync(0xffffffffu, my_src, j);
+    const int pos = __shfl_sync(0xffffffffu, my_pos, j);
+    live[j] = src >= 0;
+    n_done += live[j] ? 1 : 0;
+    const int tok = live[j] ? pos / q.k : 0;
+    const uint64_t base = q.peer_base[live[j] ? src : 0];
+    from[j] = reinterpret_cast<const uint4*>(base + q.xq_off + (size_t)tok * q.H);
+    sfrom[j] = reinterpret_cast<const float*>(base + q.xs_off) + (size_t)tok * n_kb;
+  }
+  uint4 v[kRows][kVec];
+  float sc[kRows][2];
+#pragma unroll
+  for (int j = 0; j < kRows; ++j) {
+#pragma unroll
+    for (int u = 0; u < kVec; ++u) {
+      const int i = u * 32 + lane;
+      if (live[j] && i < vec_per_row) v[j][u] = from[j][i];
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int kb = u * 32 + lane;
+      if (live[j] && kb < n_kb) sc[j][u] = sfrom[j][kb];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kRows; ++j) {
+#pragma unroll
+    for (int u = 0; u < kVec; ++u) {
+      const int i = u * 32 + lane;
+      if (live[j] && i < vec_per_row)
+        reinterpret_cast<uint4*>(q.x_out + (size_t)(r0 + j) * q.H)[i] = v[j][u];
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int kb = u * 32 + lane;
+      if (live[j] && kb < n_kb) q.scale_out[(size_t)kb * q.m_cap + r0 + j] = sc[j][u];
+    }
+  }
+  // publish: every lane's stores of these rows are ordered before the add
+  __syncwarp();
+  if (lane == 0 && n_done > 0) {
+    __threadfence();
+    red_release_gpu_add(q.arrived + r0 / 128, n_done);  // 128-row blocks of the GEMM
+  }
+  return true;
+}
+
+// `worker` of `n_workers` warps; all 32 lanes call it together. Rows are taken
+// in ascending order, so row blocks complete in the order the GEMM walks them.
+// H <= 4096: four rows per pass; H <= 8192: two (the rows wait in registers).
 __device__ __forceinline__ void pull_rows(const PullParams& q, int worker, int n_workers) {
   const int lane = threadIdx.x & 31;
   const int rows = min(max(*q.m_valid, 0), q.m_cap);
   const int n_kb = q.H / kQuantBlock;
   const int vec_per_row = q.H / 16;  // 16-byte pieces
-  for (int r0 = 2 * worker; r0 < rows; r0 += 2 * n_workers) {
-    // two rows per pass: r0 and r0 + 1 (same 128-row block)
-    int src[2], tok[2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int r = r0 + j;
-      src[j] = r < rows ? q.source_rank[r] : -1;
-      tok[j] = -1;
-      if (src[j] >= 0) {
-        int pos = 0;
-        if (lane == 0) pos = pull_wait_pos(q, r);
-        pos = __shfl_sync(0xffffffffu, pos, 0);
-        if (pos < 0) return;  // the wait ran out: reported, stop
-        tok[j] = pos / q.k;
-      }
-    }
-    const uint4* from[2];
-    const float* sfrom[2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const uint64_t base = src[j] >= 0 ? q.peer_base[src[j]] : 0;
-      from[j] = reinterpret_cast<const uint4*>(base + q.xq_off + (size_t)max(tok[j], 0) * q.H);
-      sfrom[j] = reinterpret_cast<const float*>(base + q.xs_off) + (size_t)max(tok[j], 0) * n_kb;
-    }
-    // H <= 8192: at most 16 pieces per lane per row; both rows' loads are issued
-    // before the first store
-    for (int i0 = 0; i0 < vec_per_row; i0 += 32 * 4) {
-      uint4 v[2][4];
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * 32 + lane;
-          if (tok[j] >= 0 && i < vec_per_row) v[j][u] = from[j][i];
-        }
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * 32 + lane;
-          if (tok[j] >= 0 && i < vec_per_row)
-            reinterpret_cast<uint4*>(q.x_out + (size_t)(r0 + j) * q.H)[i] = v[j][u];
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      if (tok[j] < 0) continue;
-      for (int kb = lane; kb < n_kb; kb += 32)
-        q.scale_out[(size_t)kb * q.m_cap + r0 + j] = sfrom[j][kb];
-    }
-    // publish: every lane's stores of these rows are ordered before the add
-    __syncwarp();
-    const int n_done = (tok[0] >= 0 ? 1 : 0) + (tok[1] >= 0 ? 1 : 0);
-    if (lane == 0 && n_done > 0) {
-      __threadfence();
-      red_release_gpu_add(q.arrived + r0 / 128, n_done);  // 128-row blocks of the GEMM
-    }
+  if (q.H <= 4096) {
+    for (int r0 = 4 * worker; r0 < rows; r0 += 4 * n_workers)
+      if (!pull_pass<4, 8>(q, r0, rows, n_kb, vec_per_row, lane)) return;
+  } else {
+    for (int r0 = 2 * worker; r0 < rows; r0 += 2 * n_workers)
+      if (!pull_pass<2, 16>(q, r0, rows, n_kb, vec_per_row, lane)) return;
   }
 }
 

@@ -91,7 +91,9 @@ def test_compiled_extension_exposes_reference_names(lib):
     for name in ["init", "cast", "fused_silu_mul_quant", "fp8_grouped_gemm_nt",
                  "fp8_grouped_gemm_swiglu", "fp8_grouped_gemm_swiglu_contiguous",
                  "fp8_grouped_gemm_swiglu_masked", "fp8_grouped_gemm_swiglu_sub",
-                 "fp8_grouped_gemm_swiglu_pp", "fp8_grouped_gemm_swiglu_masked_pp"]:
+                 "fp8_grouped_gemm_swiglu_pp", "fp8_grouped_gemm_swiglu_masked_pp", "bf16_gemm",
+                 "fp8_gemm_nt", "All2All", "naive_moe_forward_dispatch", "all2all_symmetric_bytes"]:
         assert hasattr(ext, name), name
+    assert ext.all2all_symmetric_bytes(256, 8, 2, 128, 1024, 1) > 0
     assert int(ext.GemmType.MGroupedContiguous) == 1 and int(ext.GemmType.MGroupedMasked) == 2
     ext.init("", "")

@@ -973,3 +973,51 @@ def test_module_all2all_reference_interface(mc, oracle_mod):
         a2a.dispatch(counts, ex, es, torch.zeros((513, H), dtype=torch.float8_e4m3fn, device=DEV),
                      torch.zeros((H // 128, 513), device=DEV),
                      torch.zeros((513, k), dtype=torch.int32, device=DEV), None)
+
+
+def test_compiled_module_all2all_and_naive_forward(mc, oracle_mod):
+    """The compiled module's All2All (C++ All2AllBase over the C-ABI context,
+    include/moe_cuda_b200_torch.hpp) and its naive_moe_forward_dispatch with the
+    reference's 21 positional arguments, one rank as its own peer: the same bits
+    as the one-GPU layer call on the same routing."""
+    from parallel_playground_b200.build import load_extension
+    from parallel_playground_b200 import workloads as wl
+    import dataclasses
+    ext = load_extension()
+    shape = dataclasses.replace(wl.CONFIGS["tiny"], T=200)
+    inp = wl.make_layer_inputs(shape)
+    d = inp.to(DEV)
+    T, H, I, E, k = shape.T, shape.H, shape.I, shape.E, shape.k
+    layer = mc.MoELayer(T, H, I, E, k, d.w_router, d.gate, d.gate_scale, d.up, d.up_scale, d.down,
+                        d.down_scale)
+    ref = torch.empty((T, H), dtype=torch.bfloat16, device=DEV)
+    layer.forward(d.x, ref)
+    idx, wts = layer.indices.clone(), layer.weights.clone()
+    sym = torch.zeros(ext.all2all_symmetric_bytes(T, E, k, 128, H, 1), dtype=torch.uint8, device=DEV)
+    a2a = ext.All2All(T, E, k, 128, H, None, torch.float8_e4m3fn, torch.bfloat16, torch.float32,
+                      device=0, peer_base=[sym.data_ptr()], rank=0)
+    M = a2a.max_recv_tokens
+    xq = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=DEV)
+    xs = torch.empty((H // 128, T), dtype=torch.float32, device=DEV)
+    mc.cast(d.x, xq, xs)
+    ex = torch.zeros((M, H), dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    es = torch.zeros((H // 128, M), dtype=torch.float32, device=DEV)
+    inter = torch.zeros((M, I), dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    inter_s = torch.zeros((I // 128, M), dtype=torch.float32, device=DEV)
+    ey = torch.zeros((M, H), dtype=torch.bfloat16, device=DEV)
+    out = torch.full((T, H), 3.0, dtype=torch.bfloat16, device=DEV)
+    ext.naive_moe_forward_dispatch(a2a, E, k, H, ext.GemmType.MGroupedContiguous, xq, xs, d.gate,
+                                   d.gate_scale, d.up, d.up_scale, d.down, d.down_scale, idx, wts, out,
+                                   ex, es, inter, inter_s, ey)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+    # the two halves through the class methods
+    counts = torch.zeros(E, dtype=torch.int32, device=DEV)
+    a2a.dispatch(counts, ex, es, xq, xs, idx, wts, do_recv=False)
+    a2a.dispatch(counts, ex, es, xq, xs, idx, wts, do_send=False)
+    out2 = torch.full_like(out, 4.0)
+    a2a.combine(out2, idx, wts, ey)
+    torch.cuda.synchronize()
+    assert torch.equal(out2.view(torch.int16), ref.view(torch.int16))
+    assert torch.equal(counts.cpu(), torch.bincount(idx.flatten().cpu().long(), minlength=E).int())
+    del a2a

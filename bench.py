@@ -54,6 +54,10 @@ def parse_args():
     ap.add_argument("--ep-fused", type=int, default=0, choices=[0, 1],
                     help="ctx transport: rows fetched by a kernel of their own before the gate/up "
                          "GEMM (0, default: measured faster) or by comm CTAs inside it (1)")
+    ap.add_argument("--ep-mode", default="auto", choices=["auto", "push", "pull"],
+                    help="ctx transport: senders store each token once per destination rank and "
+                         "the owners fan it out (push; auto picks it unless --ep-fused 1), or the "
+                         "owners load every copy (pull)")
     ap.add_argument("--no-targets", action="store_true",
                     help="skip the short runs of the other configurations (the `targets` key)")
     ap.add_argument("--no-parity", action="store_true",
@@ -367,7 +371,7 @@ def build_step(mc, args, shape, d, bias_d, dev, rank, world, fused=None):
         return build_single_gpu_step(mc, shape, d, bias_d, dev)
     if args.ep_transport == "ctx":
         return build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world,
-                                 bool(args.ep_fused) if fused is None else fused)
+                                 bool(args.ep_fused) if fused is None else fused, args.ep_mode)
     from parallel_playground_b200.ep import build_ep_step, build_ep_step_p2p
     if args.ep_transport == "p2p":
         return build_ep_step_p2p(mc, shape, d, bias_d, dev, rank, world,
@@ -376,13 +380,14 @@ def build_step(mc, args, shape, d, bias_d, dev, rank, world, fused=None):
     return build_ep_step(mc, shape, d, bias_d, dev, rank, world)
 
 
-def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused):
+def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused, mode="auto"):
     """N > 1 ranks through the C-ABI expert-parallel context: the whole layer is
     one library call per step; stage times come from CUDA events that the library
     records around its launches."""
     from parallel_playground_b200.ep import EPContext
     T, H = shape.T, shape.H
-    ctx = EPContext(T, shape.E, shape.k, H, device=dev.index)
+    ctx = EPContext(T, shape.E, shape.k, H, device=dev.index, transport=mode)
+    push = (mode != "pull") and not fused
     out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
     idx = torch.empty((T, shape.k), dtype=torch.int32, device=dev)
     wts = torch.empty((T, shape.k), dtype=torch.float32, device=dev)
@@ -410,14 +415,25 @@ def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused):
         valid = ctx.dst_rank >= 0
         return int((valid & (ctx.dst_rank != rank)).sum().item())
 
-    # cast, plan x3, exchange+plan, mark, announce, [pull,] gate/up GEMM, pos, down GEMM,
-    # barrier, reduce + router x2
-    layer = {"kernels_per_step": 14 if fused else 15, "out": out, "ctx": ctx, "run": run,
-             "routed_rows": lambda: int(ctx.tokens_per_expert.sum().item()),
+    def dispatch_rows():
+        """token rows that cross NVLink in the dispatch: one per remote copy (pull), or
+        one per (token, remote rank) (push)"""
+        if not push:
+            return remote_copies()
+        hit = torch.zeros((T, world), dtype=torch.bool, device=dev)
+        hit.scatter_(1, ctx.dst_rank.clamp(min=0).long(), ctx.dst_rank >= 0)
+        hit[:, rank] = False
+        return int(hit.sum().item())
+
+    # router x2, plan x3, exchange+plan, then push: dispatch, barrier, fan-out, transpose;
+    # pull: cast, mark, announce, pull (or inside the GEMM), pos; gate/up GEMM, down GEMM,
+    # barrier, reduce
+    layer = {"kernels_per_step": 14 if push else (15 if fused else 16), "out": out, "ctx": ctx,
+             "run": run, "routed_rows": lambda: int(ctx.tokens_per_expert.sum().item()),
              "e2e_fn": lambda x_dev, out_dev: run(x_dev, out_dev),
              "overflow": lambda: int(ctx.overflow.item()), "remote_copies": remote_copies,
-             "dispatch_rows": remote_copies, "stage_ms": stage_ms, "idx": idx, "wts": wts,
-             "fused": fused}
+             "dispatch_rows": dispatch_rows, "stage_ms": stage_ms, "idx": idx, "wts": wts,
+             "fused": fused, "push": push}
     return step, None, layer
 
 
@@ -526,13 +542,16 @@ def transport_figures(shape, world, layer, st, args):
            "nvlink_peak_gbs_per_direction": 900.0, "dispatch_ms": st.get("dispatch"),
            "combine_ms": st.get("combine"), "router_ms": st.get("router")}
     if args.ep_transport == "ctx":
-        fused = layer["fused"]
-        # the rows cross NVLink in the receive half: inside the gate/up GEMM (fused) or
-        # in the pull kernel; the results go home inside the down GEMM
-        xfer_ms = st["swiglu"] if fused else st["dispatch_recv"]
+        fused, push = layer["fused"], layer["push"]
+        # the rows cross NVLink in the send half (push: plan, count exchange and the
+        # dispatch kernel together), in the pull kernel, or inside the gate/up GEMM
+        # (fused); the results go home inside the down GEMM
+        xfer_ms = st["dispatch"] if push else (st["swiglu"] if fused else st["dispatch_recv"])
         out.update({"dispatch_fused_into_gemm": bool(fused),
+                    "dispatch_mode": "push, once per destination rank" if push else "pull, per copy",
                     "dispatch_recv_ms": st["dispatch_recv"],
-                    "dispatch_transfer_in": "swiglu_gemm" if fused else "pull kernel",
+                    "dispatch_transfer_in": ("send half (plan + count exchange + dispatch kernel)"
+                                             if push else ("swiglu_gemm" if fused else "pull kernel")),
                     "dispatch_nvlink_gbs": sent * row_b / (xfer_ms * 1e-3) / 1e9,
                     "dispatch_nvlink_frac": sent * row_b / (xfer_ms * 1e-3) / 1e9 / 900.0,
                     "dispatch_phase_ms": st["dispatch"] + st["dispatch_recv"],

@@ -375,13 +375,17 @@ int moeb_moe_forward_host(const moeb_layer_config *cfg, const void *x_bf16_host,
  * its stream work is done; the caller must let EVERY rank finish moeb_ep_create before any
  * rank dispatches (one host-side barrier at set-up; none afterwards).
  *
- * Transport. A rank quantises its tokens once (e4m3, 1x128 scales) into its symmetric
- * buffer; the per-expert counts travel with a rank-barrier kernel; every expert copy costs
- * its sender one 8-byte word stored into the owner's buffer; the owners load the rows over
- * NVLink (plain peer loads, no TMA multicast), either in a kernel of their own or, in the
- * fused form, by a few comm CTAs of the gate/up GEMM while its other CTAs already compute
- * on the 128-row blocks that have landed. Expert outputs go home inside the down GEMM's
- * store warps, then one rank barrier and a local weighted reduction. Rows of an expert are
+ * Transport. The per-expert counts travel with a rank-barrier kernel, which also plans both
+ * sides. Then either PUSH (default for bf16 tokens): the sender quantises every token once
+ * (e4m3, 1x128 scales) and stores it once per destination RANK into that rank's stash, plus
+ * one word per expert copy; after a rank barrier the owners fan the stash rows out to their
+ * experts' rows locally. Or PULL (pre-quantised tokens, and the fused form): the rank's
+ * quantised tokens sit in its symmetric buffer, every expert copy costs its sender one
+ * 8-byte word stored into the owner's buffer, and the owners load the rows over NVLink (plain
+ * peer loads, no TMA multicast) -- in a kernel of their own or, fused, by a few comm CTAs of
+ * the gate/up GEMM while its other CTAs already compute on the 128-row blocks that have
+ * landed. Expert outputs go home inside the down GEMM's store warps, then one rank barrier
+ * and a local weighted reduction. All forms deliver the same bytes in the same rows. Rows of an expert are
  * ordered (source rank, token, slot). Every device-side wait is bounded (2 s), after which
  * status_dev gets {4, role, index, tag} and the kernels run to their end.
  * One dispatch/combine pair in flight per context (all2all_tk.hpp:31-32). */
@@ -393,6 +397,7 @@ typedef struct {
   int expert_padding;  /* every local expert's rows start on a multiple of this (128) */
   int world, rank;
   int capacity_rows;   /* rows a rank can receive; 0 = worst case (all2all_tk.hpp:101-106) */
+  int transport;       /* 0 = chosen per call, 1 = always pull, 2 = always push (see below) */
 } moeb_ep_config;
 
 typedef struct moeb_ep_ctx moeb_ep_ctx;

@@ -384,7 +384,7 @@ inline std::shared_ptr<All2AllBase> make_all2all_ranked(
   detail::need(parallel_config.dp_size <= 1, "dp_size must be 1");
   moeb_ep_config cfg{(int)max_num_tokens, (int)hidden_dim,        (int)num_experts,
                      (int)experts_per_token, (int)expert_padding, (int)parallel_config.world_size,
-                     rank,                0};
+                     rank,                0,                   0};
   const size_t bytes = moeb_ep_local_bytes(&cfg);
   detail::need(bytes > 0, "bad expert-parallel configuration");
   at::Tensor ws = at::empty({(int64_t)bytes},

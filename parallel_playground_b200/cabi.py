@@ -42,7 +42,7 @@ class EpConfig(ctypes.Structure):
     """moeb_ep_config"""
     _fields_ = [("max_tokens", c_int), ("hidden", c_int), ("num_experts", c_int),
                 ("top_k", c_int), ("expert_padding", c_int), ("world", c_int), ("rank", c_int),
-                ("capacity_rows", c_int)]
+                ("capacity_rows", c_int), ("transport", c_int)]
 
 
 class EpView(ctypes.Structure):

@@ -39,13 +39,14 @@ constexpr int kTimingStages = 7;   // start, router, dispatch send, dispatch rec
 static size_t al256(size_t x) { return (x + 255) / 256 * 256; }
 
 struct SymLayout {
-  size_t flags, counts, xq, xs, pos, home, total;
+  size_t flags, counts, xq, xs, pos, home, stash_x, stash_scale, pos32p, total;
   size_t counts_stride, xq_stride, xs_stride;  // per parity
 };
 struct LocalLayout {
   size_t peer_tab, send_counts, send_offs, send_row, send_token, send_slot, send_layout, plan_ws,
       dest_base, m_valid, overflow, dst_rank, dst_row, home_row, tokens_per_expert, padded_offsets,
-      grouped_layout, source_rank, pos32, arrive_need, arrived, expert_x, scale_mn, total;
+      grouped_layout, source_rank, pos32, arrive_need, arrived, expert_x, scale_mn, scale_stage,
+      tab_stash_x, tab_stash_scale, tab_pos32p, total;
   size_t plan_ws_bytes;
 };
 
@@ -55,7 +56,8 @@ static bool ep_config_ok(const moeb_ep_config* c) {
          c->num_experts <= kEpCtxMaxExperts && c->top_k > 0 && c->top_k <= 32 &&
          c->expert_padding > 0 && c->expert_padding % 128 == 0 && c->world > 0 &&
          c->world <= kEpCtxMaxWorld && c->rank >= 0 && c->rank < c->world &&
-         c->num_experts % c->world == 0 && c->capacity_rows >= 0;
+         c->num_experts % c->world == 0 && c->capacity_rows >= 0 && c->transport >= 0 &&
+         c->transport <= 2;
 }
 
 static int ep_m_cap(const moeb_ep_config& c) {
@@ -88,6 +90,10 @@ static bool sym_layout(const moeb_ep_config& c, SymLayout* s) {
   s->xs = take(2 * s->xs_stride);
   s->pos = take((size_t)m_cap * 8);
   s->home = take((size_t)c.max_tokens * c.top_k * c.hidden * 2);
+  // push transport: one row per (source rank, token) and the senders' position words
+  s->stash_x = take((size_t)c.world * c.max_tokens * c.hidden);
+  s->stash_scale = take((size_t)c.world * c.max_tokens * n_kb * 4);
+  s->pos32p = take((size_t)m_cap * 4);
   s->total = off;
   return true;
 }
@@ -129,6 +135,10 @@ static bool local_layout(const moeb_ep_config& c, LocalLayout* l) {
   l->arrived = take(nb * 4);
   l->expert_x = take((size_t)m_cap * c.hidden);
   l->scale_mn = take((size_t)m_cap * n_kb * 4);
+  l->scale_stage = take((size_t)m_cap * n_kb * 4);
+  l->tab_stash_x = take((size_t)c.world * 8);
+  l->tab_stash_scale = take((size_t)c.world * 8);
+  l->tab_pos32p = take((size_t)c.world * 8);
   l->total = off;
   return true;
 }
@@ -172,6 +182,9 @@ struct moeb_ep_ctx {
   uint8_t* out_x;
   float* out_scale;
   int out_rows, peer_rows;
+  int transport;       // configured: 0 = by call (push for bf16 tokens, else pull), 1 = pull, 2 = push
+  bool push_cur;       // transport of the dispatch in flight
+  int32_t* pos32_cur;  // source position of every received row (local copy or the senders' words)
   // optional stage timing (host-side events, no device memory)
   bool timing;
   int timing_n;
@@ -480,8 +493,18 @@ static int set_output(moeb_ep_ctx* c, void* out_x, float* out_scale, int out_row
 // per-copy words. Afterwards the layout of this rank's rows is known; the rows
 // themselves are fetched by the receive half or by the fused GEMM.
 static int dispatch_send(moeb_ep_ctx* c, const void* x_bf16, const void* x_q, const float* x_scale_mn,
-                         const int32_t* indices, int T, int32_t* status, cudaStream_t s) {
+                         const int32_t* indices, int T, bool need_pull, int32_t* status,
+                         cudaStream_t s) {
   const moeb_ep_config& g = c->cfg;
+  // Transport of this dispatch. Push (the senders store every token once per
+  // destination rank, the owners fan it out) moves fewer bytes and is the default
+  // for bf16 tokens; pull (the owners load every copy) is what pre-quantised tokens
+  // and the dispatch fused into the GEMM use.
+  const bool push = !need_pull && x_bf16 != nullptr && c->transport != 1;
+  if (c->transport == 2 && !push) {
+    set_last_error_msg("moeb_ep_dispatch: the push transport takes bf16 tokens and is not fused");
+    return kInvalidArgument;
+  }
   if (T < 0 || T > g.max_tokens) {
     set_last_error_msg("moeb_ep_dispatch: num_tokens exceeds max_tokens");
     return kInvalidArgument;
@@ -496,7 +519,7 @@ static int dispatch_send(moeb_ep_ctx* c, const void* x_bf16, const void* x_q, co
   uint8_t* xq = c->sym_mine + c->sym.xq + par * c->sym.xq_stride;
   float* xs = reinterpret_cast<float*>(c->sym_mine + c->sym.xs + par * c->sym.xs_stride);
   int rc;
-  if (T > 0) {
+  if (T > 0 && !push) {
     if (x_bf16) {
       if ((rc = moeb_cast_bf16_to_e4m3(x_bf16, xq, xs, T, g.hidden, 0, s))) return rc;
     } else {
@@ -520,7 +543,18 @@ static int dispatch_send(moeb_ep_ctx* c, const void* x_bf16, const void* x_q, co
       at<int32_t>(L, c->loc.grouped_layout), at<int32_t>(L, c->loc.source_rank),
       at<int32_t>(L, c->loc.arrive_need), at<int32_t>(L, c->loc.arrived),
       at<int32_t>(L, c->loc.overflow), status);
-  if (T > 0) {
+  if (push) {
+    // quantise + one peer store per destination rank + one word per copy
+    if ((rc = ep_dispatch_once_home(
+             x_bf16, indices, at<const int32_t>(L, c->loc.send_row),
+             at<const int32_t>(L, c->loc.send_offs), at<const int32_t>(L, c->loc.dest_base), T,
+             g.max_tokens, g.top_k, g.hidden, g.num_experts, g.world, g.rank, c->peer_rows,
+             at<const uint64_t>(L, c->loc.tab_stash_x), at<const uint64_t>(L, c->loc.tab_stash_scale),
+             at<const uint64_t>(L, c->loc.tab_pos32p), at<int32_t>(L, c->loc.dst_rank),
+             at<int32_t>(L, c->loc.dst_row), at<int32_t>(L, c->loc.home_row),
+             at<int32_t>(L, c->loc.overflow), s)))
+      return rc;
+  } else if (T > 0) {
     const int n_pairs = T * g.top_k;
     const int blocks = ceil_div(n_pairs, 256) < 148 * 8 ? ceil_div(n_pairs, 256) : 148 * 8;
     ep_mark_invalid_kernel<<<blocks, 256, 0, s>>>(indices, n_pairs, g.num_experts,
@@ -540,8 +574,12 @@ static int dispatch_send(moeb_ep_ctx* c, const void* x_bf16, const void* x_q, co
   c->n_tokens = T;
   c->sent = true;
   c->received = false;
+  c->push_cur = push;
+  c->pos32_cur = push ? at<int32_t>(c->sym_mine, c->sym.pos32p) : at<int32_t>(L, c->loc.pos32);
   return kOk;
 }
+
+static int fence(moeb_ep_ctx* c, int32_t* status, cudaStream_t s);
 
 static int pos32_launch(moeb_ep_ctx* c, cudaStream_t s) {
   uint8_t* L = c->local;
@@ -557,6 +595,25 @@ static int dispatch_recv(moeb_ep_ctx* c, int32_t* status, cudaStream_t s) {
   if (!c->sent) {
     set_last_error_msg("moeb_ep_dispatch: the receive half needs a preceding send half");
     return kInvalidArgument;
+  }
+  if (c->push_cur) {
+    // every rank's stores have landed (rank barrier), then the owner-side fan-out
+    // of the stash rows and the scales' way to MN-major
+    uint8_t* L = c->local;
+    int rc = fence(c, status, s);
+    if (rc) return rc;
+    const int32_t* m_valid = at<const int32_t>(L, c->loc.m_valid);
+    if ((rc = moeb_ep_unstash(c->sym_mine + c->sym.stash_x,
+                              at<const float>(c->sym_mine, c->sym.stash_scale),
+                              at<const int32_t>(L, c->loc.source_rank), c->pos32_cur, m_valid,
+                              c->out_rows, c->cfg.top_k, c->cfg.max_tokens, c->cfg.hidden, c->out_x,
+                              at<float>(L, c->loc.scale_stage), s)))
+      return rc;
+    if ((rc = moeb_ep_scale_transpose(at<const float>(L, c->loc.scale_stage), m_valid, c->out_rows,
+                                      c->cfg.hidden / 128, c->out_scale, s)))
+      return rc;
+    c->received = true;
+    return kOk;
   }
   const PullParams q = make_pull(c, status);
   ep_pull_kernel<<<sm_count_ctx() * 2, 384, 0, s>>>(q);
@@ -653,6 +710,16 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
   c->timing = false;
   c->timing_n = 0;
   set_output(c, nullptr, nullptr, 0);
+  c->transport = cfg->transport;
+  if (const char* t = getenv("MOEB_EP_TRANSPORT")) c->transport = atoi(t);
+  c->push_cur = false;
+  c->pos32_cur = at<int32_t>(c->local, ll.pos32);
+  uint64_t tabs[3][kEpCtxMaxWorld];
+  for (int p = 0; p < cfg->world; ++p) {
+    tabs[0][p] = peer_base_host[p] + sl.stash_x;
+    tabs[1][p] = peer_base_host[p] + sl.stash_scale;
+    tabs[2][p] = peer_base_host[p] + sl.pos32p;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   // flags, counts and the per-row words start at zero (tag 0 = nothing yet); the
   // caller lets every rank finish this call before the first dispatch anywhere
@@ -660,6 +727,10 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
   if (err == cudaSuccess) err = cudaMemsetAsync(c->sym_mine + sl.pos, 0, sl.home - sl.pos, s);
   if (err == cudaSuccess)
     err = cudaMemcpyAsync(c->local + ll.peer_tab, c->peer_host, sizeof(uint64_t) * cfg->world,
+                          cudaMemcpyHostToDevice, s);
+  const size_t tab_off[3] = {ll.tab_stash_x, ll.tab_stash_scale, ll.tab_pos32p};
+  for (int i = 0; i < 3 && err == cudaSuccess; ++i)
+    err = cudaMemcpyAsync(c->local + tab_off[i], tabs[i], sizeof(uint64_t) * cfg->world,
                           cudaMemcpyHostToDevice, s);
   if (err == cudaSuccess) err = cudaMemsetAsync(c->local + ll.m_valid, 0, 4, s);
   if (err == cudaSuccess)   // every row starts as padding (-1)
@@ -694,7 +765,7 @@ extern "C" int moeb_ep_get_view(moeb_ep_ctx* c, moeb_ep_view* v) {
   v->tokens_per_expert = at<int32_t>(L, c->loc.tokens_per_expert);
   v->padded_offsets = at<int32_t>(L, c->loc.padded_offsets);
   v->source_rank = at<int32_t>(L, c->loc.source_rank);
-  v->source_pos = at<int32_t>(L, c->loc.pos32);
+  v->source_pos = c->pos32_cur;
   v->dst_rank = at<int32_t>(L, c->loc.dst_rank);
   v->dst_row = at<int32_t>(L, c->loc.dst_row);
   v->overflow = at<int32_t>(L, c->loc.overflow);
@@ -714,7 +785,7 @@ extern "C" int moeb_ep_dispatch(moeb_ep_ctx* c, const void* x_bf16, const void* 
   int rc;
   if (do_send) {
     if ((rc = set_output(c, out_expert_x, out_expert_x_scale, out_rows))) return rc;
-    if ((rc = dispatch_send(c, x_bf16, x_q, x_scale_mn, indices, num_tokens, status_dev, s)))
+    if ((rc = dispatch_send(c, x_bf16, x_q, x_scale_mn, indices, num_tokens, false, status_dev, s)))
       return rc;
   }
   if (do_recv && (rc = dispatch_recv(c, status_dev, s))) return rc;
@@ -738,8 +809,8 @@ extern "C" int moeb_ep_combine(moeb_ep_ctx* c, const void* expert_y_bf16, const 
     }
     ep_send_home_kernel<<<sm_count_ctx() * 8, 256, 0, s>>>(
         (const __nv_bfloat16*)expert_y_bf16, at<const int32_t>(L, c->loc.source_rank),
-        at<const int32_t>(L, c->loc.pos32), at<const int32_t>(L, c->loc.m_valid), c->out_rows,
-        c->cfg.hidden, at<const uint64_t>(L, c->loc.peer_tab), c->sym.home);
+        c->pos32_cur, at<const int32_t>(L, c->loc.m_valid), c->out_rows, c->cfg.hidden,
+        at<const uint64_t>(L, c->loc.peer_tab), c->sym.home);
     MOEB_CUDA_TRY(cudaGetLastError());
   }
   if (do_recv) return combine_recv(c, weights, out_bf16, accumulate, status_dev, s);
@@ -763,7 +834,8 @@ extern "C" int moeb_ep_fused_dispatch_swiglu(moeb_ep_ctx* c, const void* x_bf16,
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
   if ((rc = set_output(c, out_expert_x, out_expert_x_scale, out_rows))) return rc;
-  if ((rc = dispatch_send(c, x_bf16, x_q, x_scale_mn, indices, num_tokens, status_dev, s)))
+  if ((rc = dispatch_send(c, x_bf16, x_q, x_scale_mn, indices, num_tokens, fused != 0, status_dev,
+                          s)))
     return rc;
   record_stage(c, 2, s);
   uint8_t* L = c->local;
@@ -809,8 +881,8 @@ extern "C" int moeb_ep_fused_gemm_combine(moeb_ep_ctx* c, const void* A, const f
   // down projection; its store warps send every row home over NVLink
   if ((rc = fp8_gemm_nt_scatter_off(A, scale_a, down_q, down_scale,
                                     at<const uint64_t>(L, c->loc.peer_tab), c->sym.home,
-                                    at<const int32_t>(L, c->loc.source_rank),
-                                    at<const int32_t>(L, c->loc.pos32), c->out_rows,
+                                    at<const int32_t>(L, c->loc.source_rank), c->pos32_cur,
+                                    c->out_rows,
                                     at<const int32_t>(L, c->loc.m_valid), c->cfg.hidden,
                                     intermediate, c->e_local,
                                     at<const int32_t>(L, c->loc.grouped_layout), status_dev, s)))

@@ -80,7 +80,8 @@ ep_dispatch_p2p_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __res
                        const uint64_t* __restrict__ peer_pos, int32_t* __restrict__ dst_rank,
                        int32_t* __restrict__ dst_row, int32_t* __restrict__ overflow,
                        const uint64_t* __restrict__ stash_x,
-                       const uint64_t* __restrict__ stash_scale, int rank, int t_max) {
+                       const uint64_t* __restrict__ stash_scale, int rank, int t_max,
+                       int32_t* __restrict__ home_row) {
   __shared__ int rows_s[kEpMaxTopK];
   __shared__ int ranks_s[kEpMaxTopK];
   __shared__ float scales_s[kEpMaxScaleBlocks];
@@ -109,6 +110,8 @@ ep_dispatch_p2p_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __res
       ranks_s[threadIdx.x] = d;
       dst_rank[(size_t)t * k + threadIdx.x] = d;
       dst_row[(size_t)t * k + threadIdx.x] = r;
+      // row of this copy's result in the home buffer; a dropped copy has none
+      if (home_row != nullptr) home_row[(size_t)t * k + threadIdx.x] = r >= 0 ? t * k + (int)threadIdx.x : -1;
       // tell the owner where this row came from (used when its output is sent home)
       if (r >= 0 && peer_pos != nullptr)
         reinterpret_cast<int32_t*>(peer_pos[d])[r] = t * k + (int)threadIdx.x;
@@ -391,7 +394,8 @@ extern "C" int moeb_ep_dispatch_p2p(const void* x_bf16, const int32_t* indices,
   const int cap = 148 * 16;
   ep_dispatch_p2p_kernel<<<T < cap ? T : cap, threads, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x_bf16, indices, send_row, send_offsets, dest_base, T, k, H, E, W,
-      m_cap, peer_x, peer_scale, peer_pos, dst_rank, dst_row, overflow, nullptr, nullptr, 0, 0);
+      m_cap, peer_x, peer_scale, peer_pos, dst_rank, dst_row, overflow, nullptr, nullptr, 0, 0,
+      nullptr);
   MOEB_CUDA_TRY(cudaGetLastError());
   return kOk;
 }
@@ -404,6 +408,19 @@ extern "C" int moeb_ep_dispatch_once(const void* x_bf16, const int32_t* indices,
                                      const uint64_t* peer_stash_scale, const uint64_t* peer_pos,
                                      int32_t* dst_rank, int32_t* dst_row, int32_t* overflow,
                                      void* stream) {
+  return moeb::ep_dispatch_once_home(x_bf16, indices, send_row, send_offsets, dest_base, T, t_max, k,
+                                     H, E, W, rank, m_cap, peer_stash_x, peer_stash_scale, peer_pos,
+                                     dst_rank, dst_row, nullptr, overflow, (cudaStream_t)stream);
+}
+
+// moeb_ep_dispatch_once that also fills the home-row map of the push combine
+// (home_row[t*k+slot] = t*k+slot, or -1 for a dropped copy); used by ep_ctx.cu.
+int moeb::ep_dispatch_once_home(const void* x_bf16, const int32_t* indices, const int32_t* send_row,
+                                const int32_t* send_offsets, const int32_t* dest_base, int T,
+                                int t_max, int k, int H, int E, int W, int rank, int m_cap,
+                                const uint64_t* peer_stash_x, const uint64_t* peer_stash_scale,
+                                const uint64_t* peer_pos, int32_t* dst_rank, int32_t* dst_row,
+                                int32_t* home_row, int32_t* overflow, cudaStream_t stream) {
   if ((T > 0 && (!x_bf16 || !indices || !send_row || !dst_rank || !dst_row)) || !send_offsets ||
       !dest_base || !peer_stash_x || !peer_stash_scale || !peer_pos || !overflow || T < 0 ||
       T > t_max || k <= 0 || k > kEpMaxTopK || H <= 0 || H % kQuantBlock != 0 ||
@@ -419,7 +436,7 @@ extern "C" int moeb_ep_dispatch_once(const void* x_bf16, const int32_t* indices,
   ep_dispatch_p2p_kernel<<<T < cap ? T : cap, threads, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x_bf16, indices, send_row, send_offsets, dest_base, T, k, H, E, W,
       m_cap, nullptr, nullptr, peer_pos, dst_rank, dst_row, overflow, peer_stash_x,
-      peer_stash_scale, rank, t_max);
+      peer_stash_scale, rank, t_max, home_row);
   MOEB_CUDA_TRY(cudaGetLastError());
   return kOk;
 }

@@ -62,6 +62,13 @@ int fp8_gemm_nt_scatter_off(const void* A, const float* scale_a, const void* W,
                             const int32_t* m_valid_dev, int N, int K, int G,
                             const int32_t* grouped_layout, int32_t* status_dev,
                             cudaStream_t stream);
+// ep_p2p.cu: moeb_ep_dispatch_once that also fills the home-row map (-1: dropped).
+int ep_dispatch_once_home(const void* x_bf16, const int32_t* indices, const int32_t* send_row,
+                          const int32_t* send_offsets, const int32_t* dest_base, int T, int t_max,
+                          int k, int H, int E, int W, int rank, int m_cap,
+                          const uint64_t* peer_stash_x, const uint64_t* peer_stash_scale,
+                          const uint64_t* peer_pos, int32_t* dst_rank, int32_t* dst_row,
+                          int32_t* home_row, int32_t* overflow, cudaStream_t stream);
 // ep_p2p.cu: rank barrier over flag words at peer_base[p] + flags_off.
 int ep_barrier_off(const uint64_t* peer_base, size_t flags_off, int rank, int W, int channel,
                    uint32_t epoch, int32_t* status_dev, cudaStream_t stream);

@@ -147,8 +147,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("all2all_symmetric_bytes",
         [](int max_num_tokens, int num_experts, int experts_per_token, int expert_padding,
            int hidden_dim, int world_size) {
-          moeb_ep_config cfg{max_num_tokens, hidden_dim, num_experts, experts_per_token,
-                             expert_padding, world_size,  0,           0};
+          moeb_ep_config cfg{max_num_tokens, hidden_dim,  num_experts, experts_per_token,
+                             expert_padding, world_size,  0,           0,
+                             0};
           return moeb_ep_symmetric_bytes(&cfg);
         });
   py::class_<moe_cuda::All2AllBase, std::shared_ptr<moe_cuda::All2AllBase>>(m, "All2All")

@@ -679,17 +679,21 @@ class EPContext:
     torch's symmetric memory: dispatch, combine, the two fused ops and the whole
     layer are single library calls; nothing is sequenced from Python.
 
-    Transport: every rank quantises its tokens once into its symmetric buffer,
-    announces each expert copy to the owner with one 8-byte word, and the owners
-    load the rows over NVLink — in a kernel of their own (`fused=False`) or by a few
-    comm CTAs inside the gate/up GEMM while its other CTAs compute on the row
-    blocks that have landed (`fused=True`, the reference's kernel5_1 scheme).
+    Transport: push (default for bf16 tokens: every token is quantised and stored
+    once per destination rank, the owners fan it out) or pull (`transport="pull"`,
+    pre-quantised tokens, and `fused=True`: the owners load every copy over NVLink —
+    in a kernel of their own or by a few comm CTAs inside the gate/up GEMM while its
+    other CTAs compute on the row blocks that have landed, the reference's
+    kernel5_1 scheme).
 
     With world size 1 (or without an initialised process group) the rank is its
     own and only peer and a plain device buffer serves as symmetric memory."""
 
+    TRANSPORTS = {"auto": 0, "pull": 1, "push": 2}
+
     def __init__(self, max_num_tokens, num_experts, experts_per_token, hidden_dim,
-                 expert_padding=128, capacity_rows=None, device=None, group=None):
+                 expert_padding=128, capacity_rows=None, device=None, group=None,
+                 transport="auto"):
         import ctypes
         from . import moe_cuda as mc
         self._mc = mc
@@ -706,7 +710,7 @@ class EPContext:
         self.T, self.E, self.k, self.H = int(max_num_tokens), int(num_experts), \
             int(experts_per_token), int(hidden_dim)
         self.cfg = cabi.EpConfig(self.T, self.H, self.E, self.k, int(expert_padding), self._world,
-                                 self._rank, int(capacity_rows or 0))
+                                 self._rank, int(capacity_rows or 0), self.TRANSPORTS[transport])
         lib = cabi.load()
         sym_bytes = lib.moeb_ep_symmetric_bytes(ctypes.byref(self.cfg))
         loc_bytes = lib.moeb_ep_local_bytes(ctypes.byref(self.cfg))
@@ -744,7 +748,7 @@ class EPContext:
         self.tokens_per_expert = loc(v.tokens_per_expert, self.e_local, torch.int32)
         self.padded_offsets = loc(v.padded_offsets, self.e_local + 1, torch.int32)
         self.source_rank = loc(v.source_rank, self.m_cap, torch.int32)
-        self.source_pos = loc(v.source_pos, self.m_cap, torch.int32)
+        self._source_pos_local = loc(v.source_pos, self.m_cap, torch.int32)
         self.dst_rank = loc(v.dst_rank, self.T * self.k, torch.int32).view(self.T, self.k)
         self.dst_row = loc(v.dst_row, self.T * self.k, torch.int32).view(self.T, self.k)
         self.overflow = loc(v.overflow, 1, torch.int32)
@@ -762,6 +766,16 @@ class EPContext:
     rank = property(lambda self: self._rank)
     world_size = property(lambda self: self._world)
     max_recv_tokens = property(lambda self: self.m_cap)
+
+    @property
+    def source_pos(self):
+        """token*k + slot (on its source rank) of every received row of the last
+        dispatch: a local array after a pull, the senders' words after a push."""
+        v = cabi.EpView()
+        cabi.call("moeb_ep_get_view", self._ctx, self._ctypes.byref(v))
+        buf = self.local if self.local.data_ptr() <= int(v.source_pos) < \
+            self.local.data_ptr() + self.local.numel() else self.sym
+        return self._slice(buf, v.source_pos, self.m_cap, torch.int32)
 
     def _stream(self):
         return torch.cuda.current_stream().cuda_stream

@@ -71,9 +71,15 @@ def _worker(rank, world, port, q):
         layer = lambda out, fused, x=d.x: ctx.moe_forward(  # noqa: E731
             x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale, d.down, d.down_scale, out,
             shape, fused=fused)
-        for fused in (False, True, True, False, True):     # repeated: buffers alternate by step
+        pull_ctx = EPContext(T, shape.E, k, H, device=rank, transport="pull")
+        for fused in (False, True, True, False, "pull", True, "pull"):   # buffers alternate by step
             out = torch.full((T, H), 9.0, dtype=torch.bfloat16, device=dev)
-            layer(out, fused)
+            if fused == "pull":     # rows fetched by the pull kernel, not fused
+                pull_ctx.moe_forward(d.x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale,
+                                     d.down, d.down_scale, out, shape, fused=False)
+                assert torch.equal(pull_ctx.tokens_per_expert, staged._tokens_per_expert)
+            else:                   # False: push transport; True: pull inside the GEMM
+                layer(out, fused)
             torch.cuda.synchronize()
             mc.check_device_status()
             assert int(ctx.overflow.item()) == 0
@@ -213,6 +219,7 @@ def _worker(rank, world, port, q):
         assert torch.equal(bits(out6)[kept], bits(out_ref)[kept])
         small.close()
         dist.barrier()
+        pull_ctx.close()
         ctx.close()
         dist.destroy_process_group()
         q.put((rank, "ok"))
@@ -248,7 +255,25 @@ def test_ep_context_without_process_group_and_bounded_wait():
     torch.cuda.set_device(0)
     dev = torch.device("cuda:0")
     T, E, k, H = 64, 8, 2, 256
-    ctx = EPContext(T, E, k, H, device=0)
+    # the push transport first: same bytes in the same rows
+    g0 = torch.Generator().manual_seed(3)
+    x0 = torch.randn(T, H, generator=g0).bfloat16().to(dev)
+    idx0 = torch.rand(T, E, generator=g0).argsort(1)[:, :k].int().contiguous().to(dev)
+    push = EPContext(T, E, k, H, device=0, transport="push")
+    push.dispatch(x=x0, indices=idx0)
+    torch.cuda.synchronize()
+    mc.check_device_status()
+    xq0 = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=dev)
+    xs0 = torch.empty((T, H // 128), dtype=torch.float32, device=dev)
+    mc.cast(x0, xq0, xs0)
+    rows0 = push.dst_row[:T].flatten().long()
+    assert torch.equal(push.expert_x.view(torch.uint8)[rows0], xq0.view(torch.uint8).repeat_interleave(k, 0))
+    assert torch.equal(push.scale_mn.t()[rows0], xs0.repeat_interleave(k, 0))
+    assert torch.equal(push.source_pos[rows0], torch.arange(T * k, dtype=torch.int32, device=dev))
+    with pytest.raises(cabi.MoebError):       # pre-quantised tokens need the pull transport
+        push.dispatch(indices=idx0, x_q=xq0, x_scale_mn=xs0.t().contiguous())
+    push.close()
+    ctx = EPContext(T, E, k, H, device=0, transport="pull")
     assert ctx.world_size == 1 and ctx.max_recv_tokens % 128 == 0
     with pytest.raises(cabi.MoebError):
         ctx.dispatch(do_send=False, do_recv=True)

@@ -657,7 +657,7 @@ def parity_leg(mc, args, shape, inp, d, bias_d, dev, rank, world, layer):
                          "bit-identical to the staged NCCL transport"}
 
 
-TARGET_WORKLOADS = {1: ["qwen3", "mixtral", "dsv3_decode"], 2: ["qwen3"], 4: ["qwen3"],
+TARGET_WORKLOADS = {1: ["qwen3", "mixtral", "dsv3_rank", "dsv3_decode"], 2: ["qwen3"], 4: ["qwen3"],
                     8: ["dsv3_prefill", "dsv3_decode", "mixtral", "qwen3"]}
 
 
@@ -895,13 +895,30 @@ def measure_e2e(mc, layer, shape, inp, dev, world, args):
     same = same and all(torch.equal(o.view(torch.int16), layer["out"].cpu().view(torch.int16))
                         for o in ohs)
     nbytes = shape.T * shape.H * 2
+    copy_ms = copy_only_ms(tuple(inp.x.shape), dev, x_seq, o_seq)
     return {"value": shape.T / (ms * 1e-3), "unit": "tokens/s",
             "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "ms_per_step": ms,
             "serial_ms_per_step": ms_serial, "serial_value": shape.T / (ms_serial * 1e-3),
+            "copy_only_ms_per_step": copy_ms, "copy_only_value": shape.T / (copy_ms * 1e-3),
             "batches": n, "matches_device_path": bool(same),
             "api": "MoELayer.forward_host_batches (pinned host batches, copies overlapped with the "
                    "layer over the C ABI moeb_moe_forward); serial_* = one blocking "
                    "moeb_moe_forward_host call per batch"}
+
+
+def copy_only_ms(x_shape, dev, x_seq, o_seq):
+    """ms per batch of the host pipeline with the layer replaced by a device-to-device
+    copy: the ceiling the H2D + D2H copies alone allow."""
+    from parallel_playground_b200.hostpipe import HostPipeline
+    pipe = HostPipeline(lambda x, o: o.copy_(x), x_shape, x_shape, torch.bfloat16, dev)
+    pipe.process(x_seq[:4], o_seq[:4])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    pipe.process(x_seq, o_seq)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / len(x_seq)
 
 
 def measure_e2e_ep(mc, layer, shape, inp, dev, args):
@@ -926,13 +943,19 @@ def measure_e2e_ep(mc, layer, shape, inp, dev, args):
     torch.cuda.synchronize()
     mc.check_device_status()
     same = all(torch.equal(o.view(torch.int16), layer["out"].cpu().view(torch.int16)) for o in ohs)
-    t = torch.tensor([e0.elapsed_time(e1) / n, 0.0 if same else 1.0], device=dev)
+    # the same batches with the layer replaced by a device copy: what the host side of the
+    # node (PCIe switches, host memory) lets N ranks move at the same time
+    dist.barrier()
+    copy_ms = copy_only_ms(tuple(inp.x.shape), dev, x_seq, o_seq)
+    t = torch.tensor([e0.elapsed_time(e1) / n, 0.0 if same else 1.0, copy_ms], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t[0].item())
+    ms, copy_ms = float(t[0].item()), float(t[2].item())
     nbytes = shape.T * shape.H * 2
     world = dist.get_world_size()
     return {"value": shape.T * world / (ms * 1e-3), "unit": "tokens/s",
             "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "ms_per_step": ms,
+            "copy_only_ms_per_step": copy_ms,
+            "copy_only_value": shape.T * world / (copy_ms * 1e-3),
             "batches": n, "matches_device_path": bool(t[1].item() == 0.0),
             "api": "hostpipe.HostPipeline over the expert-parallel layer call of ep.py "
                    "(pinned host batches per rank, copies overlapped with the layer)"}

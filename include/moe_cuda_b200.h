@@ -397,7 +397,9 @@ typedef struct {
   int expert_padding;  /* every local expert's rows start on a multiple of this (128) */
   int world, rank;
   int capacity_rows;   /* rows a rank can receive; 0 = worst case (all2all_tk.hpp:101-106) */
-  int transport;       /* 0 = chosen per call, 1 = always pull, 2 = always push (see below) */
+  int transport;       /* 0 = push in moeb_ep_moe_forward(fused = 0), pull elsewhere; 1 = always
+                          pull; 2 = always push (bf16 tokens, not fused). Every rank must use the
+                          same value: the choice never depends on a rank's own tokens */
 } moeb_ep_config;
 
 typedef struct moeb_ep_ctx moeb_ep_ctx;

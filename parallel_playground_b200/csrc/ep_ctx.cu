@@ -183,6 +183,7 @@ struct moeb_ep_ctx {
   float* out_scale;
   int out_rows, peer_rows;
   int transport;       // configured: 0 = by call (push for bf16 tokens, else pull), 1 = pull, 2 = push
+  bool auto_push;      // set by the whole-layer call around its dispatch
   bool push_cur;       // transport of the dispatch in flight
   int32_t* pos32_cur;  // source position of every received row (local copy or the senders' words)
   // optional stage timing (host-side events, no device memory)
@@ -493,16 +494,14 @@ static int set_output(moeb_ep_ctx* c, void* out_x, float* out_scale, int out_row
 // per-copy words. Afterwards the layout of this rank's rows is known; the rows
 // themselves are fetched by the receive half or by the fused GEMM.
 static int dispatch_send(moeb_ep_ctx* c, const void* x_bf16, const void* x_q, const float* x_scale_mn,
-                         const int32_t* indices, int T, bool need_pull, int32_t* status,
+                         const int32_t* indices, int T, bool push, int32_t* status,
                          cudaStream_t s) {
   const moeb_ep_config& g = c->cfg;
-  // Transport of this dispatch. Push (the senders store every token once per
-  // destination rank, the owners fan it out) moves fewer bytes and is the default
-  // for bf16 tokens; pull (the owners load every copy) is what pre-quantised tokens
-  // and the dispatch fused into the GEMM use.
-  const bool push = !need_pull && x_bf16 != nullptr && c->transport != 1;
-  if (c->transport == 2 && !push) {
-    set_last_error_msg("moeb_ep_dispatch: the push transport takes bf16 tokens and is not fused");
+  // `push`: transport of this dispatch, chosen by the caller from the entry point
+  // and the configuration only (never from this rank's token count or pointers:
+  // every rank must take the same branch, ranks without tokens included).
+  if (push && T > 0 && !x_bf16) {
+    set_last_error_msg("moeb_ep_dispatch: the push transport takes bf16 tokens");
     return kInvalidArgument;
   }
   if (T < 0 || T > g.max_tokens) {
@@ -713,6 +712,7 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
   c->transport = cfg->transport;
   if (const char* t = getenv("MOEB_EP_TRANSPORT")) c->transport = atoi(t);
   c->push_cur = false;
+  c->auto_push = false;
   c->pos32_cur = at<int32_t>(c->local, ll.pos32);
   uint64_t tabs[3][kEpCtxMaxWorld];
   for (int p = 0; p < cfg->world; ++p) {
@@ -785,7 +785,9 @@ extern "C" int moeb_ep_dispatch(moeb_ep_ctx* c, const void* x_bf16, const void* 
   int rc;
   if (do_send) {
     if ((rc = set_output(c, out_expert_x, out_expert_x_scale, out_rows))) return rc;
-    if ((rc = dispatch_send(c, x_bf16, x_q, x_scale_mn, indices, num_tokens, false, status_dev, s)))
+    // transport: pull unless the context is configured for push
+    if ((rc = dispatch_send(c, x_bf16, x_q, x_scale_mn, indices, num_tokens, c->transport == 2,
+                            status_dev, s)))
       return rc;
   }
   if (do_recv && (rc = dispatch_recv(c, status_dev, s))) return rc;
@@ -834,8 +836,14 @@ extern "C" int moeb_ep_fused_dispatch_swiglu(moeb_ep_ctx* c, const void* x_bf16,
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
   if ((rc = set_output(c, out_expert_x, out_expert_x_scale, out_rows))) return rc;
-  if ((rc = dispatch_send(c, x_bf16, x_q, x_scale_mn, indices, num_tokens, fused != 0, status_dev,
-                          s)))
+  if (fused && c->transport == 2) {
+    set_last_error_msg("moeb_ep_fused_dispatch_swiglu: the fused form uses the pull transport");
+    return kInvalidArgument;
+  }
+  // transport: pull when fused or configured so; push when configured so, or when
+  // the whole-layer call asks for it (its tokens are always bf16)
+  const bool push = !fused && (c->transport == 2 || (c->transport == 0 && c->auto_push));
+  if ((rc = dispatch_send(c, x_bf16, x_q, x_scale_mn, indices, num_tokens, push, status_dev, s)))
     return rc;
   record_stage(c, 2, s);
   uint8_t* L = c->local;
@@ -944,10 +952,12 @@ extern "C" int moeb_ep_moe_forward(moeb_ep_ctx* c, const moeb_layer_config* cfg,
   record_stage(c, 1, s);
   // status words: [0,4) gate/up GEMM and the rows it waits for, [4,8) down GEMM,
   // [8,12) rank barrier of the combine
-  if ((rc = moeb_ep_fused_dispatch_swiglu(c, x_bf16, nullptr, nullptr, indices, T, nullptr, nullptr,
-                                          0, gate_q, gate_scale, up_q, up_scale, inter, inter_scale,
-                                          cfg->I, fused, status_dev, stream)))
-    return rc;
+  c->auto_push = true;   // bf16 tokens on every rank: the push transport unless configured otherwise
+  rc = moeb_ep_fused_dispatch_swiglu(c, x_bf16, nullptr, nullptr, indices, T, nullptr, nullptr, 0,
+                                     gate_q, gate_scale, up_q, up_scale, inter, inter_scale, cfg->I,
+                                     fused, status_dev, stream);
+  c->auto_push = false;
+  if (rc) return rc;
   if ((rc = moeb_ep_fused_gemm_combine(c, inter, inter_scale, down_q, down_scale, cfg->I, weights,
                                        out_bf16, 0, status_dev ? status_dev + 4 : nullptr, stream)))
     return rc;

@@ -48,6 +48,11 @@ CONFIGS = {
     "dsv3_decode": LayerShape("dsv3_decode", T=128, H=7168, I=2048, E=256, k=8,
                               router_mode=ROUTER_SIGMOID_GROUPED, n_group=8, topk_group=4,
                               route_scale=2.5, seed=4),
+    # one-GPU stand-in for the work of ONE rank of the DeepSeek-V3-shaped layer at EP=8:
+    # its 32 experts and as many routed rows (4096 tokens x top-8) as a rank receives
+    "dsv3_rank": LayerShape("dsv3_rank", T=4096, H=7168, I=2048, E=32, k=8,
+                            router_mode=ROUTER_SIGMOID_GROUPED, n_group=8, topk_group=4,
+                            route_scale=2.5, seed=4),
 }
 
 

@@ -241,7 +241,10 @@ def test_ep_context_matches_staged_transport_and_oracle(world):
     results = dict(q.get(timeout=600) for _ in range(world))
     for p in procs:
         p.join(timeout=60)
-    assert all(v == "ok" for v in results.values()), results
+    for r, v in sorted(results.items()):
+        if v != "ok":
+            print(f"--- rank {r}\n{v}")
+    assert all(v == "ok" for v in results.values()), sorted(results)
 
 
 def test_ep_context_without_process_group_and_bounded_wait():

@@ -26,7 +26,10 @@ SRC = ORACLE_DIR / "moe_oracle.c"
 DET_MATH_DIR = REPO_ROOT / "parallel_playground_b200" / "csrc"
 REF_DIR = ORACLE_DIR / "_ref"
 REF_BIN = REF_DIR / "ref_fixtures"
-REFERENCE_ROOT = Path(os.environ.get("MOE_REFERENCE_ROOT", "/root/reference"))
+# the reference checkout: named by MOE_REFERENCE_ROOT, else a directory `reference`
+# beside this repository (absent on machines that only run the tests)
+REFERENCE_ROOT = Path(os.environ["MOE_REFERENCE_ROOT"]) if os.environ.get("MOE_REFERENCE_ROOT") \
+    else REPO_ROOT.parent / "reference"
 
 
 def build_oracle(force: bool = False) -> Path:

@@ -109,7 +109,6 @@ struct GemmParams {
   const int32_t* arrive_cnt;   // [num_m_blocks] rows landed so far
   const int32_t* arrive_need;  // [num_m_blocks] rows the block holds
   int n_comm;
-  int comm_share_pct;  // tiles a comm CTA takes afterwards, in percent of a compute CTA's share
   PullParams pull;
 };
 
@@ -379,28 +378,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
   const int num_tiles = num_m_blocks * p.num_n_blocks;
   const int num_kb = p.K / kBK;
-  // Tiles are dealt round-robin to the CTAs. Fused dispatch: the last n_comm CTAs
-  // first fetch this rank's rows (the others already compute on the row blocks
-  // that have landed) and then work through the TAIL of the tile list, which
-  // holds the row blocks that land last; the tail is sized for the share of a
-  // compute CTA's time they have left (comm_share_pct).
-  int tile_first = (int)blockIdx.x, tile_stride = (int)gridDim.x, tile_end = num_tiles;
-  if constexpr (kFused) {
-    const int n_compute = (int)gridDim.x - p.n_comm;
-    const long long w_comm = (long long)p.n_comm * p.comm_share_pct;
-    const int tail = (int)(((long long)num_tiles * w_comm) / (100LL * n_compute + w_comm));
-    if ((int)blockIdx.x >= n_compute) {
-      pull_rows(p.pull, ((int)blockIdx.x - n_compute) * (kGemmThreads / 32) + warp,
-                p.n_comm * (kGemmThreads / 32));
-      tile_first = num_tiles - tail + ((int)blockIdx.x - n_compute);
-      tile_stride = p.n_comm;
-    } else {
-      tile_stride = n_compute;
-      tile_end = num_tiles - tail;
-    }
-  }
+  // tiles are dealt round-robin to the CTAs that run the GEMM
+  const int tile_stride = (int)gridDim.x - (kFused ? p.n_comm : 0);
 
-  if (warp < 4) {
+  if (kFused && (int)blockIdx.x >= tile_stride) {
+    // ------------------------------------------------ comm CTA: pull rows --
+    pull_rows(p.pull, ((int)blockIdx.x - tile_stride) * (kGemmThreads / 32) + warp,
+              p.n_comm * (kGemmThreads / 32));
+  } else if (warp < 4) {
     setmaxnreg_dec<kRegsProducerWg>();
     if (warp == 0) {
       // ------------------------------------------------------ TMA producer --
@@ -409,7 +394,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       bool ok = true;
       // (the producer and MMA warps run on 40 registers: they use the plain tile
       // loop; only the promotion warps prefetch the next tile's layout word)
-      for (int tile = tile_first; tile < tile_end && ok; tile += tile_stride) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_stride) {
         const TileInfo ti = get_tile(p, tile);
         if (!ti.valid) continue;
         const int a_row = ti.m_block * kBM;
@@ -450,7 +435,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       int stage = 0, buf = 0;
       uint32_t phase = 0, bphase = 0;
       bool ok = true;
-      for (int tile = tile_first; tile < tile_end && ok; tile += tile_stride) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_stride) {
         const TileInfo ti = get_tile(p, tile);
         if (!ti.valid) continue;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -491,7 +476,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       // l+64, l+96. Down projection: one warp per column half (warps 2 and 3).
       const int h = warp - 2;
       uint32_t sphase = 0;
-      for (int tile = tile_first; tile < tile_end; tile += tile_stride) {
+      for (int tile = blockIdx.x; tile < num_tiles; tile += tile_stride) {
         const TileInfo ti = get_tile(p, tile);
         if (!ti.valid) continue;
         if (!mbar_wait_bounded(staged_bar(h), sphase, abort_flag, p.wait_hint_ns)) {
@@ -582,17 +567,17 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
     TileWalker w;
     w.stride = tile_stride;
     EpiTile et{};
-    int tile = tile_first;
+    int tile = blockIdx.x;
     if constexpr (kTileLookAhead) {
-      w.seek(p, tile_first, tile_end);
-      if (w.tile < tile_end) et = open_tile(w.ti);
+      w.seek(p, blockIdx.x, num_tiles);
+      if (w.tile < num_tiles) et = open_tile(w.ti);
       tile = w.tile;
     }
-    while (tile < tile_end && ok) {
+    while (tile < num_tiles && ok) {
       TileInfo ti;
       if constexpr (kTileLookAhead) {
         ti = w.ti;
-        w.prefetch(p, tile_end);
+        w.prefetch(p, num_tiles);
       } else {
         ti = get_tile(p, tile);
         if (!ti.valid) {
@@ -679,8 +664,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       // `up` accumulators are free (opened earlier, the extra live values spill).
       EpiTile et_next{};
       if constexpr (kTileLookAhead && kEarly && !kSwiglu) {
-        w.advance(p, tile_end);
-        if (w.tile < tile_end) et_next = open_tile(w.ti);
+        w.advance(p, num_tiles);
+        if (w.tile < num_tiles) et_next = open_tile(w.ti);
       }
 
       // ------------------------------------------------------- tile epilogue --
@@ -707,8 +692,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
           amax = fmaxf(amax, fabsf(y));
         }
         if constexpr (kTileLookAhead && kEarly) {
-          w.advance(p, tile_end);
-          if (w.tile < tile_end) et_next = open_tile(w.ti);
+          w.advance(p, num_tiles);
+          if (w.tile < num_tiles) et_next = open_tile(w.ti);
         }
         float* xchg = amax_x + tile_parity * 256;
         xchg[h * 128 + row_in_tile] = amax;
@@ -867,8 +852,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
         tile = w.tile;
       } else if constexpr (kTileLookAhead) {
         // next tile (its layout word was requested at the start of this one)
-        w.advance(p, tile_end);
-        if (w.tile < tile_end) et = open_tile(w.ti);
+        w.advance(p, num_tiles);
+        if (w.tile < num_tiles) et = open_tile(w.ti);
         tile = w.tile;
       } else {
         tile += tile_stride;
@@ -1390,11 +1375,6 @@ int moeb::fp8_swiglu_fused_dispatch(const void* A, const float* scale_a, const v
   p.arrive_cnt = arrive_cnt;
   p.arrive_need = arrive_need;
   p.n_comm = n_comm;
-  static const int share_env = [] {
-    const char* e = getenv("MOEB_EP_COMM_SHARE_PCT");
-    return e ? atoi(e) : 60;
-  }();
-  p.comm_share_pct = share_env < 0 ? 0 : (share_env > 100 ? 100 : share_env);
   p.pull = pull;
   p.pull.status = status_dev;
   return launch_grouped_gemm<true>(A, gate, up, p, stream);

@@ -32,7 +32,8 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REFERENCE = Path(os.environ.get("MOE_REFERENCE_ROOT", "/root/reference"))
+REFERENCE = Path(os.environ["MOE_REFERENCE_ROOT"]) if os.environ.get("MOE_REFERENCE_ROOT") \
+    else REPO.parent / "reference"
 OUT = HERE / "reference_vectors.npz"
 
 _NP = {1: np.uint8, 2: np.uint16, 4: np.float32, 8: np.float64}

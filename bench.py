@@ -124,6 +124,11 @@ class ClockSampler:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                  "-i", str(self.gpu), "-lms", "20"], stdout=self.fh, stderr=subprocess.DEVNULL)
+            # the first sample can take a while on a box with many GPUs: the timed
+            # region must not start (and end) before the sampler is up
+            t_end = time.perf_counter() + 3.0
+            while time.perf_counter() < t_end and self.path.stat().st_size == 0:
+                time.sleep(0.02)
         except OSError:
             self.proc = None
 

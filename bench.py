@@ -433,7 +433,11 @@ def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused, mode="auto"
     # router x2, plan x3, exchange+plan, then push: dispatch, barrier, fan-out, transpose;
     # pull: cast, mark, announce, pull (or inside the GEMM), pos; gate/up GEMM, down GEMM,
     # barrier, reduce
+    # both GEMMs side by side (the library's default for W > 1 when the dispatch is not fused)
+    down_sms = int(os.environ.get("MOEB_EP_DOWN_SMS", "52"))
+    overlapped = (not fused) and 0 < down_sms <= 120
     layer = {"kernels_per_step": 14 if push else (15 if fused else 16), "out": out, "ctx": ctx,
+             "mlp_overlapped": overlapped, "down_sms": down_sms if overlapped else 0,
              "run": run, "routed_rows": lambda: int(ctx.tokens_per_expert.sum().item()),
              "e2e_fn": lambda x_dev, out_dev: run(x_dev, out_dev),
              "overflow": lambda: int(ctx.overflow.item()), "remote_copies": remote_copies,
@@ -489,7 +493,7 @@ def collect_stages(stage_events, layer):
     return out
 
 
-def gemm_figures(shape, world, rows, st, peaks, fp8):
+def gemm_figures(shape, world, rows, st, peaks, fp8, overlapped=False, down_sms=0):
     """TFLOP/s of the two grouped GEMMs and their roofline records. The launches
     are timed one by one with CUDA events inside a timed region of well under two
     seconds, so the denominator is the BURST rate of cuBLASLt's e4m3 GEMM measured
@@ -522,6 +526,16 @@ def gemm_figures(shape, world, rows, st, peaks, fp8):
                       "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})"})
         return r
 
+    if overlapped:
+        # expert parallel: the two kernels run at the same time on disjoint SMs (the down
+        # kernel follows gate/up row block by row block and feeds NVLink meanwhile); only
+        # their common span is meaningful: swiglu = gate/up kernel, down = what is left
+        # of the down kernel after gate/up has ended
+        both = record(f"gate/up and down grouped GEMMs side by side ({148 - down_sms} + {down_sms} SMs)",
+                      6.0 * rows * H * I, st["swiglu"] + st["down"],
+                      3.0 * e_local * I * H + rows * (H + 4.0 * (H // 128) + 2.0 * I +
+                                                      8.0 * (I // 128) + 2.0 * H))
+        return both, None
     up = record("grouped_gemm_fp8_kernel<swiglu> (gate/up + SwiGLU + requant)",
                 4.0 * rows * H * I, st["swiglu"],
                 2.0 * e_local * I * H + rows * (H + 4.0 * (H // 128) + I + 4.0 * (I // 128)))
@@ -552,6 +566,7 @@ def transport_figures(shape, world, layer, st, args):
         # dispatch kernel together), in the pull kernel, or inside the gate/up GEMM
         # (fused); the results go home inside the down GEMM
         xfer_ms = st["dispatch"] if push else (st["swiglu"] if fused else st["dispatch_recv"])
+        comb_ms = st["down"] + (st["swiglu"] if layer.get("mlp_overlapped") else 0.0)
         out.update({"dispatch_fused_into_gemm": bool(fused),
                     "dispatch_mode": "push, once per destination rank" if push else "pull, per copy",
                     "dispatch_recv_ms": st["dispatch_recv"],
@@ -560,9 +575,10 @@ def transport_figures(shape, world, layer, st, args):
                     "dispatch_nvlink_gbs": sent * row_b / (xfer_ms * 1e-3) / 1e9,
                     "dispatch_nvlink_frac": sent * row_b / (xfer_ms * 1e-3) / 1e9 / 900.0,
                     "dispatch_phase_ms": st["dispatch"] + st["dispatch_recv"],
-                    "combine_transfer_in": "down_gemm",
-                    "combine_nvlink_gbs": remote * 2.0 * H / (st["down"] * 1e-3) / 1e9,
-                    "combine_nvlink_frac": remote * 2.0 * H / (st["down"] * 1e-3) / 1e9 / 900.0})
+                    "combine_transfer_in": ("down kernel beside the gate/up kernel (both spans)"
+                                            if layer.get("mlp_overlapped") else "down_gemm"),
+                    "combine_nvlink_gbs": remote * 2.0 * H / (comb_ms * 1e-3) / 1e9,
+                    "combine_nvlink_frac": remote * 2.0 * H / (comb_ms * 1e-3) / 1e9 / 900.0})
         return out
     push = args.ep_transport == "p2p" and args.ep_combine == "push"
     xfer_ms = st["down"] if push else st["combine"]
@@ -682,13 +698,13 @@ def run_target(mc, args, name, world, rank, local_rank, dev, peaks, fp8):
         st = collect_stages(ev, layer)
         rows = int(layer["routed_rows"]())
         if rank == 0:
-            up, dn = gemm_figures(shape, world, rows, st, peaks, fp8)
+            up, dn = gemm_figures(shape, world, rows, st, peaks, fp8,
+                                  layer.get("mlp_overlapped", False), layer.get("down_sms", 0))
+            keys = ("kernel", "bound", "achieved", "unit", "frac", "peak", "ms_per_launch",
+                    "frac_of_nominal")
             rec = {"ms_per_step": ms_step, "tokens_per_s": shape.T * world / (ms_step * 1e-3),
-                   "routed_rows": rows, "gate_up": {k_: up[k_] for k_ in
-                                                    ("bound", "achieved", "unit", "frac", "peak",
-                                                     "ms_per_launch", "frac_of_nominal")},
-                   "down": {k_: dn[k_] for k_ in ("bound", "achieved", "unit", "frac", "peak",
-                                                  "ms_per_launch", "frac_of_nominal")},
+                   "routed_rows": rows, "gate_up": {k_: up[k_] for k_ in keys},
+                   "down": None if dn is None else {k_: dn[k_] for k_ in keys},
                    "layer_tflops": 6.0 * rows * shape.H * shape.I / (ms_step * 1e-3) / 1e12}
             if world > 1:
                 rec["transport"] = transport_figures(shape, world, layer, st, args)
@@ -751,7 +767,9 @@ def run_b200(args):
         if "ctx" in layer:
             layer["ctx"].close()
         del step, stage_events, d, bias_d
-        layer = {"kernels_per_step": layer["kernels_per_step"]}
+        layer = {"kernels_per_step": layer["kernels_per_step"],
+                 "mlp_overlapped": layer.get("mlp_overlapped", False),
+                 "down_sms": layer.get("down_sms", 0)}
         import gc
         gc.collect()
         torch.cuda.empty_cache()
@@ -763,7 +781,8 @@ def run_b200(args):
             dist.barrier()
             dist.destroy_process_group()
         return 0 if (parity is None or parity["ok"]) else 1
-    up, dn = gemm_figures(shape, world, rows, st, peaks, fp8)
+    overlapped = layer.get("mlp_overlapped", False)
+    up, dn = gemm_figures(shape, world, rows, st, peaks, fp8, overlapped, layer.get("down_sms", 0))
     line = {
         "metric": "moe_layer_tokens_per_s", "value": tokens_per_s, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -777,8 +796,9 @@ def run_b200(args):
         "roofline": up,
         "roofline_down": dn,
         "stages": {"swiglu_gemm_ms": st["swiglu"], "down_gemm_ms": st["down"],
-                   "down_gemm_tflops": 2.0 * rows * H * I / (st["down"] * 1e-3) / 1e12,
-                   "routed_rows": rows,
+                   "down_gemm_tflops": (None if overlapped else
+                                        2.0 * rows * H * I / (st["down"] * 1e-3) / 1e12),
+                   "mlp_overlapped": overlapped, "routed_rows": rows,
                    "layer_tflops": 6.0 * rows * H * I / (ms_step * 1e-3) / 1e12},
     }
     if transport is not None:

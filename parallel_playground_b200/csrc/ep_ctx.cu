@@ -45,7 +45,8 @@ struct SymLayout {
 struct LocalLayout {
   size_t peer_tab, send_counts, send_offs, send_row, send_token, send_slot, send_layout, plan_ws,
       dest_base, m_valid, overflow, dst_rank, dst_row, home_row, tokens_per_expert, padded_offsets,
-      grouped_layout, source_rank, pos32, arrive_need, arrived, expert_x, scale_mn, scale_stage,
+      grouped_layout, source_rank, pos32, arrive_need, arrived, inter_done, expert_x, scale_mn,
+      scale_stage,
       tab_stash_x, tab_stash_scale, tab_pos32p, total;
   size_t plan_ws_bytes;
 };
@@ -133,6 +134,7 @@ static bool local_layout(const moeb_ep_config& c, LocalLayout* l) {
   l->pos32 = take((size_t)m_cap * 4);
   l->arrive_need = take(nb * 4);
   l->arrived = take(nb * 4);
+  l->inter_done = take(nb * 4);
   l->expert_x = take((size_t)m_cap * c.hidden);
   l->scale_mn = take((size_t)m_cap * n_kb * 4);
   l->scale_stage = take((size_t)m_cap * n_kb * 4);
@@ -186,6 +188,10 @@ struct moeb_ep_ctx {
   bool auto_push;      // set by the whole-layer call around its dispatch
   bool push_cur;       // transport of the dispatch in flight
   int32_t* pos32_cur;  // source position of every received row (local copy or the senders' words)
+  // second stream and events for the overlapped MLP (host-side objects)
+  cudaStream_t aux;
+  cudaEvent_t ev_fork, ev_join;
+  int down_ctas;       // SMs of the down kernel when both GEMMs run side by side; 0 = one after the other
   // optional stage timing (host-side events, no device memory)
   bool timing;
   int timing_n;
@@ -234,8 +240,8 @@ ep_exchange_plan_kernel(const uint64_t* __restrict__ peer_base, size_t flags_off
                         int32_t* __restrict__ m_valid, int32_t* __restrict__ tokens_per_expert,
                         int32_t* __restrict__ padded_offsets, int32_t* __restrict__ grouped_layout,
                         int32_t* __restrict__ source_rank, int32_t* __restrict__ arrive_need,
-                        int32_t* __restrict__ arrived, int32_t* __restrict__ overflow,
-                        int32_t* __restrict__ status) {
+                        int32_t* __restrict__ arrived, int32_t* __restrict__ inter_done,
+                        int32_t* __restrict__ overflow, int32_t* __restrict__ status) {
   extern __shared__ int xp_smem[];
   int* tot = xp_smem;      // [E]
   int* poff = tot + E;     // [E] padded offset inside the owner's layout
@@ -335,6 +341,7 @@ ep_exchange_plan_kernel(const uint64_t* __restrict__ peer_base, size_t flags_off
     if (lane == 0) {
       arrive_need[b] = c;
       arrived[b] = 0;
+      inter_done[b] = 0;   // gate/up tiles finished per block (overlapped MLP)
     }
   }
 }
@@ -541,7 +548,7 @@ static int dispatch_send(moeb_ep_ctx* c, const void* x_bf16, const void* x_q, co
       at<int32_t>(L, c->loc.tokens_per_expert), at<int32_t>(L, c->loc.padded_offsets),
       at<int32_t>(L, c->loc.grouped_layout), at<int32_t>(L, c->loc.source_rank),
       at<int32_t>(L, c->loc.arrive_need), at<int32_t>(L, c->loc.arrived),
-      at<int32_t>(L, c->loc.overflow), status);
+      at<int32_t>(L, c->loc.inter_done), at<int32_t>(L, c->loc.overflow), status);
   if (push) {
     // quantise + one peer store per destination rank + one word per copy
     if ((rc = ep_dispatch_once_home(
@@ -709,6 +716,22 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
   c->timing = false;
   c->timing_n = 0;
   set_output(c, nullptr, nullptr, 0);
+  c->aux = nullptr;
+  c->ev_fork = c->ev_join = nullptr;
+  // Both expert GEMMs side by side (W > 1): the down kernel gets about its share of
+  // the MLP's work in SMs (a third of the FLOPs, and it also feeds NVLink).
+  c->down_ctas = cfg->world > 1 ? 52 : 0;
+  if (const char* o = getenv("MOEB_EP_DOWN_SMS")) c->down_ctas = atoi(o);
+  if (c->down_ctas < 0 || c->down_ctas > 120) c->down_ctas = 0;
+  if (c->down_ctas > 0) {
+    if (cudaStreamCreateWithFlags(&c->aux, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+      set_last_error_msg("moeb_ep_create: could not create the second stream");
+      delete c;
+      return kCudaError;
+    }
+  }
   c->transport = cfg->transport;
   if (const char* t = getenv("MOEB_EP_TRANSPORT")) c->transport = atoi(t);
   c->push_cur = false;
@@ -748,6 +771,9 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
 
 extern "C" int moeb_ep_destroy(moeb_ep_ctx* ctx) {
   if (!ctx) return kOk;
+  if (ctx->aux) cudaStreamDestroy(ctx->aux);
+  if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+  if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
   if (ctx->timing)
     for (int i = 0; i < kTimingSlots; ++i)
       for (int j = 0; j < kTimingStages; ++j) cudaEventDestroy(ctx->ev[i][j]);
@@ -952,15 +978,42 @@ extern "C" int moeb_ep_moe_forward(moeb_ep_ctx* c, const moeb_layer_config* cfg,
   record_stage(c, 1, s);
   // status words: [0,4) gate/up GEMM and the rows it waits for, [4,8) down GEMM,
   // [8,12) rank barrier of the combine
-  c->auto_push = true;   // bf16 tokens on every rank: the push transport unless configured otherwise
-  rc = moeb_ep_fused_dispatch_swiglu(c, x_bf16, nullptr, nullptr, indices, T, nullptr, nullptr, 0,
-                                     gate_q, gate_scale, up_q, up_scale, inter, inter_scale, cfg->I,
-                                     fused, status_dev, stream);
-  c->auto_push = false;
-  if (rc) return rc;
-  if ((rc = moeb_ep_fused_gemm_combine(c, inter, inter_scale, down_q, down_scale, cfg->I, weights,
-                                       out_bf16, 0, status_dev ? status_dev + 4 : nullptr, stream)))
-    return rc;
+  if (!fused && c->down_ctas > 0) {
+    // dispatch, then both GEMMs side by side: the down kernel (on its own SMs) follows
+    // the gate/up kernel row block by row block and sends its rows home meanwhile
+    uint8_t* L = c->local;
+    if ((rc = set_output(c, nullptr, nullptr, 0))) return rc;
+    if ((rc = dispatch_send(c, x_bf16, nullptr, nullptr, indices, T, c->transport != 1, status_dev,
+                            s)))
+      return rc;
+    record_stage(c, 2, s);
+    if ((rc = dispatch_recv(c, status_dev, s))) return rc;
+    record_stage(c, 3, s);
+    cudaEvent_t mid = (c->timing && c->timing_n < kTimingSlots) ? c->ev[c->timing_n][4] : nullptr;
+    if ((rc = fp8_mlp_overlapped(
+             c->out_x, c->out_scale, gate_q, gate_scale, up_q, up_scale, inter, inter_scale, down_q,
+             down_scale, at<const uint64_t>(L, c->loc.peer_tab), c->sym.home,
+             at<const int32_t>(L, c->loc.source_rank), c->pos32_cur, c->out_rows,
+             at<const int32_t>(L, c->loc.m_valid), cfg->I, H, c->e_local,
+             at<const int32_t>(L, c->loc.grouped_layout), at<int32_t>(L, c->loc.inter_done),
+             c->down_ctas, status_dev, status_dev ? status_dev + 4 : nullptr, s, c->aux, c->ev_fork,
+             c->ev_join, mid)))
+      return rc;
+    record_stage(c, 5, s);
+    if ((rc = combine_recv(c, weights, out_bf16, 0, status_dev ? status_dev + 8 : nullptr, s)))
+      return rc;
+  } else {
+    c->auto_push = true;   // bf16 tokens on every rank: the push transport unless configured otherwise
+    rc = moeb_ep_fused_dispatch_swiglu(c, x_bf16, nullptr, nullptr, indices, T, nullptr, nullptr, 0,
+                                       gate_q, gate_scale, up_q, up_scale, inter, inter_scale,
+                                       cfg->I, fused, status_dev, stream);
+    c->auto_push = false;
+    if (rc) return rc;
+    if ((rc = moeb_ep_fused_gemm_combine(c, inter, inter_scale, down_q, down_scale, cfg->I, weights,
+                                         out_bf16, 0, status_dev ? status_dev + 4 : nullptr,
+                                         stream)))
+      return rc;
+  }
   record_stage(c, 6, s);
   if (c->timing && c->timing_n < kTimingSlots) c->timing_n += 1;
   if (indices_out && T > 0)

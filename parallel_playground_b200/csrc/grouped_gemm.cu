@@ -110,6 +110,13 @@ struct GemmParams {
   const int32_t* arrive_need;  // [num_m_blocks] rows the block holds
   int n_comm;
   PullParams pull;
+  // Overlapped MLP (expert parallel): the gate/up kernel counts its finished tiles
+  // per row block (publish_cnt), the down kernel, running beside it on other SMs,
+  // waits until a row block has all its arrive_need_const tiles before it reads the
+  // block (arrive_cnt = that array, arrive_need = nullptr). max_ctas > 0 bounds the grid.
+  int32_t* publish_cnt;
+  int arrive_need_const;
+  int max_ctas;
 };
 
 struct TileInfo {
@@ -279,12 +286,14 @@ __device__ __forceinline__ void fma_chunk(float2 (&acc)[64], const uint32_t (&v)
 // tanh.approx instead of ex2 + rcp (half the special-function work of the SwiGLU
 // epilogue).
 // kOptFused: dispatch fused into the GEMM (see GemmParams::arrive_cnt).
-constexpr int kOptOffload = 1, kOptEarly = 2, kOptTanh = 4, kOptFused = 8;
+// kOptPublish: the gate/up store warp counts finished tiles per row block for a
+// down kernel that runs at the same time (GemmParams::publish_cnt).
+constexpr int kOptOffload = 1, kOptEarly = 2, kOptTanh = 4, kOptFused = 8, kOptPublish = 16;
 // Fused dispatch: wait (bounded) until all rows of a 128-row block have been
 // published by the comm CTAs. Every lane of the warp polls the same word.
 __device__ __forceinline__ bool wait_rows_arrived(const GemmParams& p, int m_block,
                                                   volatile int* abort_flag) {
-  const int need = __ldg(p.arrive_need + m_block);
+  const int need = p.arrive_need != nullptr ? __ldg(p.arrive_need + m_block) : p.arrive_need_const;
   if (ld_acquire_gpu_s32(p.arrive_cnt + m_block) >= need) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
@@ -311,6 +320,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
   constexpr bool kEarly = (kOpt & kOptEarly) != 0;
   constexpr bool kTanh = (kOpt & kOptTanh) != 0;
   constexpr bool kFused = (kOpt & kOptFused) != 0;
+  constexpr bool kPublish = (kOpt & kOptPublish) != 0;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -511,6 +521,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
         __syncwarp();
         if (lane == 0) mbar_arrive(stage_free_bar(h));
         sphase ^= 1u;
+        if constexpr (kPublish) {
+          // the tile (rows by the copies above, scales by the promotion warps before
+          // they signalled) is in global memory: count it for the down kernel
+          bulk_wait_group0();
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) red_release_gpu_add(p.publish_cnt + ti.m_block, 1);
+        }
       }
       bulk_wait_group0();          // every row has reached global memory
     }
@@ -1247,6 +1265,9 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
       // dispatch fused into this launch: n_comm CTAs pull rows, the rest compute
       kernel = grouped_gemm_fp8_kernel<true, false, kOptTanh | kOptFused>;
       n_comm = p.n_comm;
+    } else if (p.publish_cnt != nullptr) {
+      // a down kernel runs beside this launch and waits for its row blocks
+      kernel = grouped_gemm_fp8_kernel<true, false, kOptTanh | kOptOffload | kOptPublish>;
     }
   } else {
     // bf16 output, local or to peers: rows are staged in shared memory and leave
@@ -1254,6 +1275,9 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
     if (p.scatter_out != nullptr || !p.out_f32) {
       kernel = plain ? grouped_gemm_fp8_kernel<false, true, 0>
                      : grouped_gemm_fp8_kernel<false, true, kOptOffload | kOptEarly>;
+      // beside a gate/up kernel that is still producing its input: wait per row block
+      if (p.arrive_cnt != nullptr)
+        kernel = grouped_gemm_fp8_kernel<false, true, kOptOffload | kOptEarly | kOptFused>;
       smem_bytes = kGemmSmemBytesScatter;
     }
   }
@@ -1264,7 +1288,8 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
   const long long tiles = (long long)p.num_m_blocks * p.num_n_blocks;
   // every CTA must be resident at once in the fused form (compute CTAs wait for
   // comm CTAs): one CTA per SM, never more CTAs than SMs
-  const int compute_sms = sm_count() - n_comm;
+  int compute_sms = sm_count() - n_comm;
+  if (p.max_ctas > 0 && p.max_ctas < compute_sms) compute_sms = p.max_ctas;
   const int grid = (int)(tiles < compute_sms ? tiles : compute_sms) + n_comm;
   kernel<<<grid, kGemmThreads, smem_bytes, stream>>>(tm_a, tm_b0, tm_b1, p);
   MOEB_CUDA_TRY(cudaGetLastError());
@@ -1378,6 +1403,76 @@ int moeb::fp8_swiglu_fused_dispatch(const void* A, const float* scale_a, const v
   p.pull = pull;
   p.pull.status = status_dev;
   return launch_grouped_gemm<true>(A, gate, up, p, stream);
+}
+
+// Both expert GEMMs of a rank at the same time, on disjoint sets of SMs, for the
+// expert-parallel layer: the gate/up kernel (stream `main`) counts its finished
+// tiles per 128-row block; the down kernel (stream `aux`, n_down_ctas CTAs) waits for
+// a block's I/128 tiles before it reads the block and sends its rows home over
+// NVLink while gate/up is still computing later blocks, so that the link is busy
+// during the whole MLP instead of during the down projection only. `inter_done`
+// ([m_total/128] int32) must be zero. The caller has made `aux` wait for `main` up to
+// this point (ev_fork) and joins it afterwards (ev_join).
+int moeb::fp8_mlp_overlapped(const void* A, const float* scale_a, const void* gate,
+                             const float* scale_gate, const void* up, const float* scale_up,
+                             void* D, float* scale_d, const void* down, const float* scale_down,
+                             const uint64_t* peer_out, size_t home_off, const int32_t* row_rank,
+                             const int32_t* row_pos, int m_total, const int32_t* m_valid_dev,
+                             int I, int H, int G, const int32_t* grouped_layout,
+                             int32_t* inter_done, int n_down_ctas, int32_t* status_swiglu,
+                             int32_t* status_down, cudaStream_t main, cudaStream_t aux,
+                             cudaEvent_t ev_fork, cudaEvent_t ev_join, cudaEvent_t ev_gate_up_done) {
+  int rc = check_common("fp8_mlp_overlapped", A, scale_a, gate, scale_gate, D, m_total, I, H, G,
+                        MOEB_GEMM_M_GROUPED_CONTIGUOUS, grouped_layout, 0);
+  if (rc != kOk) return rc;
+  if (!up || !scale_up || !scale_d || !down || !scale_down || !peer_out || !row_rank || !row_pos ||
+      !inter_done || !m_valid_dev || n_down_ctas <= 0 || n_down_ctas >= sm_count() ||
+      !aligned16(up) || !aligned16(down)) {
+    set_last_error_msg("fp8_mlp_overlapped: bad argument");
+    return kInvalidArgument;
+  }
+  GemmParams g{};
+  g.scale_a = scale_a;
+  g.scale_b0 = scale_gate;
+  g.scale_b1 = scale_up;
+  g.out = D;
+  g.scale_d = scale_d;
+  g.layout = grouped_layout;
+  g.status = status_swiglu;
+  g.m_total = m_total;
+  g.N = I;
+  g.K = H;
+  g.G = G;
+  g.m_valid = m_valid_dev;
+  g.publish_cnt = inter_done;
+  g.max_ctas = sm_count() - n_down_ctas;
+  GemmParams d{};
+  d.scale_a = scale_d;
+  d.scale_b0 = scale_down;
+  d.scale_b1 = scale_down;
+  d.layout = grouped_layout;
+  d.status = status_down;
+  d.m_total = m_total;
+  d.N = H;
+  d.K = I;
+  d.G = G;
+  d.m_valid = m_valid_dev;
+  d.scatter_out = peer_out;
+  d.scatter_off = home_off;
+  d.scatter_rank = row_rank;
+  d.scatter_pos = row_pos;
+  d.arrive_cnt = inter_done;
+  d.arrive_need = nullptr;
+  d.arrive_need_const = I / 128;
+  d.max_ctas = n_down_ctas;
+  MOEB_CUDA_TRY(cudaEventRecord(ev_fork, main));
+  MOEB_CUDA_TRY(cudaStreamWaitEvent(aux, ev_fork, 0));
+  if ((rc = launch_grouped_gemm<true>(A, gate, up, g, main)) != kOk) return rc;
+  if (ev_gate_up_done != nullptr) MOEB_CUDA_TRY(cudaEventRecord(ev_gate_up_done, main));
+  if ((rc = launch_grouped_gemm<false>(D, down, down, d, aux)) != kOk) return rc;
+  MOEB_CUDA_TRY(cudaEventRecord(ev_join, aux));
+  MOEB_CUDA_TRY(cudaStreamWaitEvent(main, ev_join, 0));
+  return kOk;
 }
 
 extern "C" int moeb_fp8_grouped_gemm_nt(const void* A, const float* scale_a, const void* W,

@@ -71,6 +71,20 @@ def _worker(rank, world, port, q):
         layer = lambda out, fused, x=d.x: ctx.moe_forward(  # noqa: E731
             x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale, d.down, d.down_scale, out,
             shape, fused=fused)
+        # (a context made with MOEB_EP_DOWN_SMS=0 runs the two GEMMs one after the other;
+        # the default for more than one rank runs them side by side; 40 forces that form
+        # on a single rank too)
+        os.environ["MOEB_EP_DOWN_SMS"] = "0" if world > 1 else "40"
+        other_mlp = EPContext(T, shape.E, k, H, device=rank)
+        os.environ.pop("MOEB_EP_DOWN_SMS")
+        for _ in range(2):
+            out = torch.full((T, H), 8.0, dtype=torch.bfloat16, device=dev)
+            other_mlp.moe_forward(d.x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale,
+                                  d.down, d.down_scale, out, shape, fused=False)
+            torch.cuda.synchronize()
+            mc.check_device_status()
+            assert torch.equal(bits(out), bits(out_ref))
+        other_mlp.close()
         pull_ctx = EPContext(T, shape.E, k, H, device=rank, transport="pull")
         for fused in (False, True, True, False, "pull", True, "pull"):   # buffers alternate by step
             out = torch.full((T, H), 9.0, dtype=torch.bfloat16, device=dev)

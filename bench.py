@@ -433,8 +433,8 @@ def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused, mode="auto"
     # router x2, plan x3, exchange+plan, then push: dispatch, barrier, fan-out, transpose;
     # pull: cast, mark, announce, pull (or inside the GEMM), pos; gate/up GEMM, down GEMM,
     # barrier, reduce
-    # both GEMMs side by side (the library's default for W > 1 when the dispatch is not fused)
-    down_sms = int(os.environ.get("MOEB_EP_DOWN_SMS", "52"))
+    # both GEMMs side by side on disjoint SMs: an option of the library (MOEB_EP_DOWN_SMS)
+    down_sms = int(os.environ.get("MOEB_EP_DOWN_SMS", "0"))
     overlapped = (not fused) and 0 < down_sms <= 120
     layer = {"kernels_per_step": 14 if push else (15 if fused else 16), "out": out, "ctx": ctx,
              "mlp_overlapped": overlapped, "down_sms": down_sms if overlapped else 0,

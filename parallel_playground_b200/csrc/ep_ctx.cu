@@ -718,9 +718,12 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
   set_output(c, nullptr, nullptr, 0);
   c->aux = nullptr;
   c->ev_fork = c->ev_join = nullptr;
-  // Both expert GEMMs side by side (W > 1): the down kernel gets about its share of
-  // the MLP's work in SMs (a third of the FLOPs, and it also feeds NVLink).
-  c->down_ctas = cfg->world > 1 ? 52 : 0;
+  // Both expert GEMMs side by side on disjoint SMs (MOEB_EP_DOWN_SMS = SMs of the down
+  // kernel): off by default. Measured at 4 ranks on the default workload: 1.62 ms for
+  // the two GEMMs side by side (64 SMs for the down kernel; 52: 1.62, 40: 2.06) against
+  // 1.57 ms one after the other: an SM that stores its rows over NVLink is held back
+  // by its own stores (about 4 GB/s per SM either way), not by the link's total.
+  c->down_ctas = 0;
   if (const char* o = getenv("MOEB_EP_DOWN_SMS")) c->down_ctas = atoi(o);
   if (c->down_ctas < 0 || c->down_ctas > 120) c->down_ctas = 0;
   if (c->down_ctas > 0) {

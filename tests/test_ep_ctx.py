@@ -71,10 +71,9 @@ def _worker(rank, world, port, q):
         layer = lambda out, fused, x=d.x: ctx.moe_forward(  # noqa: E731
             x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale, d.down, d.down_scale, out,
             shape, fused=fused)
-        # (a context made with MOEB_EP_DOWN_SMS=0 runs the two GEMMs one after the other;
-        # the default for more than one rank runs them side by side; 40 forces that form
-        # on a single rank too)
-        os.environ["MOEB_EP_DOWN_SMS"] = "0" if world > 1 else "40"
+        # the two expert GEMMs side by side on disjoint SMs (an option; the default runs
+        # them one after the other): same bits
+        os.environ["MOEB_EP_DOWN_SMS"] = "40"
         other_mlp = EPContext(T, shape.E, k, H, device=rank)
         os.environ.pop("MOEB_EP_DOWN_SMS")
         for _ in range(2):

@@ -433,10 +433,16 @@ def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused, mode="auto"
     # router x2, plan x3, exchange+plan, then push: dispatch, barrier, fan-out, transpose;
     # pull: cast, mark, announce, pull (or inside the GEMM), pos; gate/up GEMM, down GEMM,
     # barrier, reduce
-    # both GEMMs side by side on disjoint SMs: an option of the library (MOEB_EP_DOWN_SMS)
-    down_sms = int(os.environ.get("MOEB_EP_DOWN_SMS", "0"))
-    overlapped = (not fused) and 0 < down_sms <= 120
-    layer = {"kernels_per_step": 14 if push else (15 if fused else 16), "out": out, "ctx": ctx,
+    # how the library runs the two expert GEMMs of the whole-layer call: one after the
+    # other, or overlapped (row chunks / two kernels side by side, see moeb_ep_mlp_mode)
+    mlp_mode = "seq" if fused else ctx.mlp_mode
+    overlapped = mlp_mode != "seq"
+    down_sms = int(os.environ.get("MOEB_EP_DOWN_SMS", "52"))
+    chunks = int(os.environ.get("MOEB_EP_MLP_CHUNKS", "4"))
+    # chunked: one plan kernel and two GEMM launches per chunk instead of two launches
+    extra = 2 * chunks - 1 if mlp_mode == "chunks" else 0
+    layer = {"kernels_per_step": (14 if push else (15 if fused else 16)) + extra, "out": out,
+             "ctx": ctx, "mlp_mode": mlp_mode, "mlp_chunks": chunks if mlp_mode == "chunks" else 0,
              "mlp_overlapped": overlapped, "down_sms": down_sms if overlapped else 0,
              "run": run, "routed_rows": lambda: int(ctx.tokens_per_expert.sum().item()),
              "e2e_fn": lambda x_dev, out_dev: run(x_dev, out_dev),
@@ -527,11 +533,12 @@ def gemm_figures(shape, world, rows, st, peaks, fp8, overlapped=False, down_sms=
         return r
 
     if overlapped:
-        # expert parallel: the two kernels run at the same time on disjoint SMs (the down
-        # kernel follows gate/up row block by row block and feeds NVLink meanwhile); only
-        # their common span is meaningful: swiglu = gate/up kernel, down = what is left
-        # of the down kernel after gate/up has ended
-        both = record(f"gate/up and down grouped GEMMs side by side ({148 - down_sms} + {down_sms} SMs)",
+        # expert parallel: the two GEMMs run at the same time on disjoint SMs (in row
+        # chunks, or as two kernels with the down kernel following row block by row block;
+        # the down rows feed NVLink meanwhile); only their common span is meaningful:
+        # swiglu = up to the end of gate/up, down = what is left of the down projection
+        both = record("grouped_gemm_fp8_kernel: gate/up and down GEMMs overlapped "
+                      f"({148 - down_sms} + {down_sms} SMs while both run)",
                       6.0 * rows * H * I, st["swiglu"] + st["down"],
                       3.0 * e_local * I * H + rows * (H + 4.0 * (H // 128) + 2.0 * I +
                                                       8.0 * (I // 128) + 2.0 * H))
@@ -575,7 +582,7 @@ def transport_figures(shape, world, layer, st, args):
                     "dispatch_nvlink_gbs": sent * row_b / (xfer_ms * 1e-3) / 1e9,
                     "dispatch_nvlink_frac": sent * row_b / (xfer_ms * 1e-3) / 1e9 / 900.0,
                     "dispatch_phase_ms": st["dispatch"] + st["dispatch_recv"],
-                    "combine_transfer_in": ("down kernel beside the gate/up kernel (both spans)"
+                    "combine_transfer_in": ("down projection beside gate/up (both spans)"
                                             if layer.get("mlp_overlapped") else "down_gemm"),
                     "combine_nvlink_gbs": remote * 2.0 * H / (comb_ms * 1e-3) / 1e9,
                     "combine_nvlink_frac": remote * 2.0 * H / (comb_ms * 1e-3) / 1e9 / 900.0})
@@ -769,6 +776,7 @@ def run_b200(args):
         del step, stage_events, d, bias_d
         layer = {"kernels_per_step": layer["kernels_per_step"],
                  "mlp_overlapped": layer.get("mlp_overlapped", False),
+                 "mlp_mode": layer.get("mlp_mode", "seq"), "mlp_chunks": layer.get("mlp_chunks", 0),
                  "down_sms": layer.get("down_sms", 0)}
         import gc
         gc.collect()
@@ -798,7 +806,8 @@ def run_b200(args):
         "stages": {"swiglu_gemm_ms": st["swiglu"], "down_gemm_ms": st["down"],
                    "down_gemm_tflops": (None if overlapped else
                                         2.0 * rows * H * I / (st["down"] * 1e-3) / 1e12),
-                   "mlp_overlapped": overlapped, "routed_rows": rows,
+                   "mlp_overlapped": overlapped, "mlp_mode": layer.get("mlp_mode", "seq"),
+                   "mlp_chunks": layer.get("mlp_chunks", 0), "routed_rows": rows,
                    "layer_tflops": 6.0 * rows * H * I / (ms_step * 1e-3) / 1e12},
     }
     if transport is not None:

@@ -69,6 +69,21 @@ const char *moeb_last_error(void);
 int moeb_router_logits(const void *x_bf16, const void *w_gate_bf16, const float *logit_bias,
                        float *logits, int T, int H, int E, void *stream);
 
+/* The same product with a caller-provided scratch buffer. With many tokens and more than
+ * 64 experts (E % 8 == 0) the contraction bounds the kernels behind moeb_router_logits;
+ * with a workspace of moeb_router_logits_workspace_bytes(T, H, E) bytes (256-byte aligned)
+ * the logits are computed on the tcgen05 tensor cores instead: w_gate transposed to
+ * K-major, a bf16 GEMM with its K range split over the SMs, and the slices' fp32 partial
+ * sums added in a fixed order (bit-reproducible; the sums differ from moeb_router_logits'
+ * in the last bits, as any two accumulation orders do). The size query returns 0 where
+ * that path does not apply; with no or too small a workspace the call is
+ * moeb_router_logits. x and logits must be 16-byte aligned. status_dev: optional int32[4]
+ * of the GEMM's bounded waits. */
+size_t moeb_router_logits_workspace_bytes(int T, int H, int E);
+int moeb_router_logits_ws(const void *x_bf16, const void *w_gate_bf16, const float *logit_bias,
+                          float *logits, int T, int H, int E, void *workspace,
+                          size_t workspace_bytes, int32_t *status_dev, void *stream);
+
 /* Select on given fp32 logits. Ties go to the lower expert id.
  * SOFTMAX:  top-k by logit, w_j = exp(l_j - max) / sum over the selected
  *           (renorm != 0) or over all experts (renorm == 0), times route_scale.
@@ -499,6 +514,18 @@ int moeb_ep_moe_forward(moeb_ep_ctx *ctx, const moeb_layer_config *cfg, const vo
  * barrier + reduction} and the number of calls, and starts a new series. */
 int moeb_ep_set_timing(moeb_ep_ctx *ctx, int enable);
 int moeb_ep_read_timing(moeb_ep_ctx *ctx, float *stage_ms6, int *steps);
+
+/* How moeb_ep_moe_forward (fused = 0) runs the two expert GEMMs on this context:
+ * 0 = one after the other; 1 = in row chunks, the down projection of a chunk (whose rows
+ * go home over NVLink) on a part of the SMs beside the gate/up GEMM of the next chunk;
+ * 2 = two whole kernels side by side, the down kernel following row block by row block.
+ * All three give the same bits. Chosen when the context is made: 1 with more than one
+ * rank, else 0; the environment variable MOEB_EP_MLP (seq | chunks | beside) overrides,
+ * MOEB_EP_MLP_CHUNKS (2..8, default 4) and MOEB_EP_DOWN_SMS (default 52) size modes 1, 2.
+ * With modes 1 and 2 the stage times read "gate/up GEMM" up to the end of the last
+ * gate/up launch and "down GEMM" for what is left of the down projection after it.
+ * Returns the mode, or -1 without a context. */
+int moeb_ep_mlp_mode(const moeb_ep_ctx *ctx);
 
 #ifdef __cplusplus
 }

@@ -62,6 +62,9 @@ PROTOTYPES = {
     "moeb_last_error": (ctypes.c_char_p, []),
     "moeb_router_logits": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                    c_void_p]),
+    "moeb_router_logits_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "moeb_router_logits_ws": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                      c_void_p, c_size_t, c_void_p, c_void_p]),
     "moeb_router_select": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_float, c_void_p, c_void_p, c_void_p]),
     "moeb_route_plan_rows": (c_int, [c_int, c_int, c_int, c_int]),
@@ -154,6 +157,7 @@ PROTOTYPES = {
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                     c_int, c_void_p, c_void_p]),
+    "moeb_ep_mlp_mode": (c_int, [c_void_p]),
     "moeb_ep_set_timing": (c_int, [c_void_p, c_int]),
     "moeb_ep_read_timing": (c_int, [c_void_p, ctypes.POINTER(c_float), ctypes.POINTER(c_int)]),
 }

@@ -18,16 +18,18 @@ void set_last_error(const char* what, cudaError_t e) {
   snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", what, cudaGetErrorName(e),
            cudaGetErrorString(e));
 }
+thread_local int tl_status_scopes = 0;
+
 void set_last_error_msg(const char* msg) {
   snprintf(g_last_error, sizeof(g_last_error), "%s", msg);
 }
 
 // Workspace carving for moeb_moe_forward; every region is 256-byte aligned.
 struct LayerWorkspace {
-  size_t logits, indices, weights, counts, offsets, dst_row, src_token, src_slot, layout, plan_ws,
-      expert_x, expert_x_scale, inter, inter_scale, expert_y, total;
+  size_t logits, router_ws, indices, weights, counts, offsets, dst_row, src_token, src_slot, layout,
+      plan_ws, expert_x, expert_x_scale, inter, inter_scale, expert_y, total;
   int m_cap;
-  size_t plan_ws_bytes;
+  size_t plan_ws_bytes, router_ws_bytes;
 };
 
 static size_t align256(size_t x) { return (x + 255) / 256 * 256; }
@@ -48,6 +50,8 @@ static bool carve(const moeb_layer_config& c, LayerWorkspace* w) {
   };
   const size_t n_pairs = (size_t)c.T * c.k;
   w->logits = take((size_t)c.T * c.E * 4);
+  w->router_ws_bytes = moeb_router_logits_workspace_bytes(c.T, c.H, c.E);
+  w->router_ws = take(w->router_ws_bytes);
   w->indices = take(n_pairs * 4);
   w->weights = take(n_pairs * 4);
   w->counts = take((size_t)c.E * 4);
@@ -133,7 +137,12 @@ extern "C" int moeb_moe_forward(const moeb_layer_config* cfg, const void* x_bf16
   void* expert_y = ws + w.expert_y;
 
   int rc;
-  if ((rc = moeb_router_logits(x_bf16, w_router_bf16, router_bias, logits, c.T, c.H, c.E, stream))) return rc;
+  // status words: [0,4) router GEMM (when it runs on the tensor cores) and gate/up GEMM,
+  // [4,8) down GEMM
+  StatusScope status_scope(status_dev, 8, (cudaStream_t)stream);
+  if ((rc = moeb_router_logits_ws(x_bf16, w_router_bf16, router_bias, logits, c.T, c.H, c.E,
+                                  ws + w.router_ws, w.router_ws_bytes, status_dev, stream)))
+    return rc;
   if ((rc = moeb_router_select(logits, c.T, c.E, c.k, c.router_mode, c.n_group, c.topk_group,
                                c.renorm, c.route_scale, indices, weights, stream)))
     return rc;

@@ -49,6 +49,31 @@ struct DeviceStatus {
 void set_last_error(const char* what, cudaError_t e);
 void set_last_error_msg(const char* msg);
 
+// Device status words (first report wins, see report_timeout). A kernel launcher called on
+// its own clears its four words before the launch. A call that strings several launches
+// together (a whole layer, a dispatch + GEMM) opens a StatusScope instead: the outermost
+// scope clears all the caller's words once, and no launcher inside it clears anything, so
+// that a report of an early launch (a rank barrier that ran out, the router's GEMM) is not
+// wiped by a later one that shares its words.
+extern thread_local int tl_status_scopes;
+inline bool status_scope_open() { return tl_status_scopes > 0; }
+struct StatusScope {
+  StatusScope(int32_t* status, int words, cudaStream_t s) {
+    if (tl_status_scopes == 0 && status != nullptr) cudaMemsetAsync(status, 0, sizeof(int32_t) * words, s);
+    ++tl_status_scopes;
+  }
+  ~StatusScope() { --tl_status_scopes; }
+  StatusScope(const StatusScope&) = delete;
+  StatusScope& operator=(const StatusScope&) = delete;
+};
+
+// grouped_gemm.cu: dense bf16 GEMM (tcgen05) with the K range split into slices, fp32
+// partial sums per slice at D + s * m_total * N; bf16_splitk_slices: the slices a request
+// for `want` really gets (every slice holds at least one 64-element K block).
+int bf16_gemm_splitk_f32(const void* A, const void* B, float* D, int m_total, int N, int K,
+                         int k_splits, int32_t* status_dev, cudaStream_t s);
+int bf16_splitk_slices(int K, int want);
+
 constexpr int kQuantBlock = 128;       // activation scale granularity (1 x 128)
 constexpr float kFp8Max = 448.0f;      // e4m3fn finite maximum
 

@@ -134,7 +134,7 @@ static bool local_layout(const moeb_ep_config& c, LocalLayout* l) {
   l->pos32 = take((size_t)m_cap * 4);
   l->arrive_need = take(nb * 4);
   l->arrived = take(nb * 4);
-  l->inter_done = take(nb * 4);
+  l->inter_done = take((nb > 16 ? nb : 16) * 4);   // (also the chunk plan of the chunked MLP: 2 x 8 words)
   l->expert_x = take((size_t)m_cap * c.hidden);
   l->scale_mn = take((size_t)m_cap * n_kb * 4);
   l->scale_stage = take((size_t)m_cap * n_kb * 4);
@@ -147,7 +147,7 @@ static bool local_layout(const moeb_ep_config& c, LocalLayout* l) {
 
 // Workspace of the whole-layer call (depends on the expert width I).
 struct LayerWs {
-  size_t logits, indices, weights, inter, inter_scale, total;
+  size_t logits, router_ws, router_ws_bytes, indices, weights, inter, inter_scale, total;
 };
 static void layer_ws(const moeb_ep_config& c, int m_cap, int I, LayerWs* w) {
   const size_t pairs = (size_t)c.max_tokens * c.top_k;
@@ -158,6 +158,8 @@ static void layer_ws(const moeb_ep_config& c, int m_cap, int I, LayerWs* w) {
     return at;
   };
   w->logits = take((size_t)c.max_tokens * c.num_experts * 4);
+  w->router_ws_bytes = moeb_router_logits_workspace_bytes(c.max_tokens, c.hidden, c.num_experts);
+  w->router_ws = take(w->router_ws_bytes);
   w->indices = take(pairs * 4);
   w->weights = take(pairs * 4);
   w->inter = take((size_t)m_cap * I);
@@ -190,8 +192,10 @@ struct moeb_ep_ctx {
   int32_t* pos32_cur;  // source position of every received row (local copy or the senders' words)
   // second stream and events for the overlapped MLP (host-side objects)
   cudaStream_t aux;
-  cudaEvent_t ev_fork, ev_join;
-  int down_ctas;       // SMs of the down kernel when both GEMMs run side by side; 0 = one after the other
+  cudaEvent_t ev_fork, ev_join, ev_chunk[8];
+  int mlp_mode;        // whole-layer call: 0 = GEMMs one after the other, 1 = in row chunks, 2 = side by side
+  int mlp_chunks;      // row chunks of mode 1
+  int down_ctas;       // SMs of the down kernel while a gate/up kernel runs beside it (modes 1 and 2)
   // optional stage timing (host-side events, no device memory)
   bool timing;
   int timing_n;
@@ -718,18 +722,35 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
   set_output(c, nullptr, nullptr, 0);
   c->aux = nullptr;
   c->ev_fork = c->ev_join = nullptr;
-  // Both expert GEMMs side by side on disjoint SMs (MOEB_EP_DOWN_SMS = SMs of the down
-  // kernel): off by default. Measured at 4 ranks on the default workload: 1.62 ms for
-  // the two GEMMs side by side (64 SMs for the down kernel; 52: 1.62, 40: 2.06) against
-  // 1.57 ms one after the other: an SM that stores its rows over NVLink is held back
-  // by its own stores (about 4 GB/s per SM either way), not by the link's total.
-  c->down_ctas = 0;
+  // How the whole-layer call runs the two expert GEMMs (MOEB_EP_MLP = seq | chunks |
+  // beside). With more than one rank the down projection is bound by NVLink (most of
+  // its rows go to other ranks) and the link idles during gate/up. "chunks" (default
+  // for W > 1) splits the rows into MOEB_EP_MLP_CHUNKS ranges and runs the down
+  // projection of a range, on MOEB_EP_DOWN_SMS SMs, beside the gate/up GEMM of the next
+  // one. "beside" runs two whole kernels side by side, the down kernel waiting per row
+  // block for the gate/up kernel; measured at 4 ranks on the default workload it is no
+  // faster than "seq" (1.62 against 1.57 ms: its gate/up kernel carries a store warp
+  // that costs what the overlap wins).
+  c->mlp_mode = cfg->world > 1 ? 1 : 0;
+  if (const char* o = getenv("MOEB_EP_MLP")) {
+    if (!strcmp(o, "seq") || !strcmp(o, "0")) c->mlp_mode = 0;
+    else if (!strcmp(o, "chunks")) c->mlp_mode = 1;
+    else if (!strcmp(o, "beside")) c->mlp_mode = 2;
+  }
+  c->mlp_chunks = 4;
+  if (const char* o = getenv("MOEB_EP_MLP_CHUNKS")) c->mlp_chunks = atoi(o);
+  if (c->mlp_chunks < 2 || c->mlp_chunks > 8) c->mlp_chunks = 4;
+  c->down_ctas = 52;
   if (const char* o = getenv("MOEB_EP_DOWN_SMS")) c->down_ctas = atoi(o);
-  if (c->down_ctas < 0 || c->down_ctas > 120) c->down_ctas = 0;
-  if (c->down_ctas > 0) {
-    if (cudaStreamCreateWithFlags(&c->aux, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+  if (c->down_ctas <= 0 || c->down_ctas > 120) c->down_ctas = 52;
+  for (int i = 0; i < 8; ++i) c->ev_chunk[i] = nullptr;
+  if (c->mlp_mode != 0) {
+    bool ok = cudaStreamCreateWithFlags(&c->aux, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
+              cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; ok && i < 8; ++i)
+      ok = cudaEventCreateWithFlags(&c->ev_chunk[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) {
       set_last_error_msg("moeb_ep_create: could not create the second stream");
       delete c;
       return kCudaError;
@@ -777,6 +798,8 @@ extern "C" int moeb_ep_destroy(moeb_ep_ctx* ctx) {
   if (ctx->aux) cudaStreamDestroy(ctx->aux);
   if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
   if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
+  for (int i = 0; i < 8; ++i)
+    if (ctx->ev_chunk[i]) cudaEventDestroy(ctx->ev_chunk[i]);
   if (ctx->timing)
     for (int i = 0; i < kTimingSlots; ++i)
       for (int j = 0; j < kTimingStages; ++j) cudaEventDestroy(ctx->ev[i][j]);
@@ -864,6 +887,7 @@ extern "C" int moeb_ep_fused_dispatch_swiglu(moeb_ep_ctx* c, const void* x_bf16,
   }
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
+  StatusScope status_scope(status_dev, 4, s);
   if ((rc = set_output(c, out_expert_x, out_expert_x_scale, out_rows))) return rc;
   if (fused && c->transport == 2) {
     set_last_error_msg("moeb_ep_fused_dispatch_swiglu: the fused form uses the pull transport");
@@ -915,6 +939,7 @@ extern "C" int moeb_ep_fused_gemm_combine(moeb_ep_ctx* c, const void* A, const f
   cudaStream_t s = (cudaStream_t)stream;
   uint8_t* L = c->local;
   int rc;
+  StatusScope status_scope(status_dev, 4, s);   // (the barrier's words [4,8) stick)
   // down projection; its store warps send every row home over NVLink
   if ((rc = fp8_gemm_nt_scatter_off(A, scale_a, down_q, down_scale,
                                     at<const uint64_t>(L, c->loc.peer_tab), c->sym.home,
@@ -969,9 +994,13 @@ extern "C" int moeb_ep_moe_forward(moeb_ep_ctx* c, const moeb_layer_config* cfg,
   float* inter_scale = at<float>(ws, w.inter_scale);
   const int T = cfg->T, H = cfg->H;
   int rc;
+  // (the rank barrier's words [8,12) are never cleared here: its first report sticks)
+  StatusScope status_scope(status_dev, 8, s);
   record_stage(c, 0, s);
   if (T > 0) {
-    if ((rc = moeb_router_logits(x_bf16, w_router_bf16, router_bias, logits, T, H, g.num_experts, s)))
+    if ((rc = moeb_router_logits_ws(x_bf16, w_router_bf16, router_bias, logits, T, H,
+                                    g.num_experts, ws + w.router_ws, w.router_ws_bytes, status_dev,
+                                    s)))
       return rc;
     if ((rc = moeb_router_select(logits, T, g.num_experts, g.top_k, cfg->router_mode, cfg->n_group,
                                  cfg->topk_group, cfg->renorm, cfg->route_scale, indices, weights,
@@ -981,9 +1010,11 @@ extern "C" int moeb_ep_moe_forward(moeb_ep_ctx* c, const moeb_layer_config* cfg,
   record_stage(c, 1, s);
   // status words: [0,4) gate/up GEMM and the rows it waits for, [4,8) down GEMM,
   // [8,12) rank barrier of the combine
-  if (!fused && c->down_ctas > 0) {
-    // dispatch, then both GEMMs side by side: the down kernel (on its own SMs) follows
-    // the gate/up kernel row block by row block and sends its rows home meanwhile
+  if (!fused && c->mlp_mode != 0) {
+    // dispatch, then the two GEMMs overlapped: in row chunks (the down projection of a
+    // chunk beside the gate/up GEMM of the next one), or as two whole kernels side by
+    // side with the down kernel following row block by row block; either way the down
+    // kernel's rows go home over NVLink while gate/up is still computing
     uint8_t* L = c->local;
     if ((rc = set_output(c, nullptr, nullptr, 0))) return rc;
     if ((rc = dispatch_send(c, x_bf16, nullptr, nullptr, indices, T, c->transport != 1, status_dev,
@@ -993,15 +1024,27 @@ extern "C" int moeb_ep_moe_forward(moeb_ep_ctx* c, const moeb_layer_config* cfg,
     if ((rc = dispatch_recv(c, status_dev, s))) return rc;
     record_stage(c, 3, s);
     cudaEvent_t mid = (c->timing && c->timing_n < kTimingSlots) ? c->ev[c->timing_n][4] : nullptr;
-    if ((rc = fp8_mlp_overlapped(
-             c->out_x, c->out_scale, gate_q, gate_scale, up_q, up_scale, inter, inter_scale, down_q,
-             down_scale, at<const uint64_t>(L, c->loc.peer_tab), c->sym.home,
-             at<const int32_t>(L, c->loc.source_rank), c->pos32_cur, c->out_rows,
-             at<const int32_t>(L, c->loc.m_valid), cfg->I, H, c->e_local,
-             at<const int32_t>(L, c->loc.grouped_layout), at<int32_t>(L, c->loc.inter_done),
-             c->down_ctas, status_dev, status_dev ? status_dev + 4 : nullptr, s, c->aux, c->ev_fork,
-             c->ev_join, mid)))
-      return rc;
+    if (c->mlp_mode == 1) {
+      // (the row-block counters of the side-by-side form hold the chunk plan here)
+      rc = fp8_mlp_chunked(c->out_x, c->out_scale, gate_q, gate_scale, up_q, up_scale, inter,
+                           inter_scale, down_q, down_scale, at<const uint64_t>(L, c->loc.peer_tab),
+                           c->sym.home, at<const int32_t>(L, c->loc.source_rank), c->pos32_cur,
+                           c->out_rows, at<const int32_t>(L, c->loc.m_valid), cfg->I, H, c->e_local,
+                           at<const int32_t>(L, c->loc.grouped_layout),
+                           at<int32_t>(L, c->loc.inter_done), c->mlp_chunks, c->down_ctas,
+                           status_dev, status_dev ? status_dev + 4 : nullptr, s, c->aux,
+                           c->ev_fork, c->ev_join, c->ev_chunk, mid);
+    } else {
+      rc = fp8_mlp_overlapped(
+          c->out_x, c->out_scale, gate_q, gate_scale, up_q, up_scale, inter, inter_scale, down_q,
+          down_scale, at<const uint64_t>(L, c->loc.peer_tab), c->sym.home,
+          at<const int32_t>(L, c->loc.source_rank), c->pos32_cur, c->out_rows,
+          at<const int32_t>(L, c->loc.m_valid), cfg->I, H, c->e_local,
+          at<const int32_t>(L, c->loc.grouped_layout), at<int32_t>(L, c->loc.inter_done),
+          c->down_ctas, status_dev, status_dev ? status_dev + 4 : nullptr, s, c->aux, c->ev_fork,
+          c->ev_join, mid);
+    }
+    if (rc) return rc;
     record_stage(c, 5, s);
     if ((rc = combine_recv(c, weights, out_bf16, 0, status_dev ? status_dev + 8 : nullptr, s)))
       return rc;
@@ -1027,6 +1070,8 @@ extern "C" int moeb_ep_moe_forward(moeb_ep_ctx* c, const moeb_layer_config* cfg,
                                   cudaMemcpyDeviceToDevice, s));
   return kOk;
 }
+
+extern "C" int moeb_ep_mlp_mode(const moeb_ep_ctx* c) { return c ? c->mlp_mode : -1; }
 
 extern "C" int moeb_ep_set_timing(moeb_ep_ctx* c, int enable) {
   if (!c) return kInvalidArgument;

@@ -117,6 +117,13 @@ struct GemmParams {
   int32_t* publish_cnt;
   int arrive_need_const;
   int max_ctas;
+  // Chunked MLP: optional device word, first row of this launch's range (a multiple of
+  // 128 * group_m); the range ends at *m_valid. Row blocks before it are not visited.
+  const int32_t* m_begin;
+  // bf16 kernel, dense fp32 output only: the K range is cut into k_splits slices of
+  // kb_per_split 64-element blocks; slice s of a tile is an item of its own and writes
+  // its partial sums to out + s * m_total * N (summed by the caller). 0 / 1: no split.
+  int k_splits, kb_per_split;
 };
 
 struct TileInfo {
@@ -167,6 +174,14 @@ __device__ __forceinline__ TileInfo make_tile(const GemmParams& p, int tile, int
     t.valid = m_in < key;
     t.rows_valid = min(kBM, key - m_in);
   }
+  return t;
+}
+
+// First tile of this CTA: a launch over a row range starts at the range's first row
+// block. Evaluated where a role's tile loop starts (nothing stays live in the loops).
+__device__ __forceinline__ int first_tile_of(const GemmParams& p) {
+  int t = blockIdx.x;
+  if (p.m_begin != nullptr) t += (max(__ldg(p.m_begin), 0) / kBM) * p.num_n_blocks;
   return t;
 }
 
@@ -404,7 +419,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       bool ok = true;
       // (the producer and MMA warps run on 40 registers: they use the plain tile
       // loop; only the promotion warps prefetch the next tile's layout word)
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_stride) {
+      for (int tile = first_tile_of(p); tile < num_tiles && ok; tile += tile_stride) {
         const TileInfo ti = get_tile(p, tile);
         if (!ti.valid) continue;
         const int a_row = ti.m_block * kBM;
@@ -445,7 +460,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       int stage = 0, buf = 0;
       uint32_t phase = 0, bphase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += tile_stride) {
+      for (int tile = first_tile_of(p); tile < num_tiles && ok; tile += tile_stride) {
         const TileInfo ti = get_tile(p, tile);
         if (!ti.valid) continue;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -486,7 +501,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
       // l+64, l+96. Down projection: one warp per column half (warps 2 and 3).
       const int h = warp - 2;
       uint32_t sphase = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += tile_stride) {
+      for (int tile = first_tile_of(p); tile < num_tiles; tile += tile_stride) {
         const TileInfo ti = get_tile(p, tile);
         if (!ti.valid) continue;
         if (!mbar_wait_bounded(staged_bar(h), sphase, abort_flag, p.wait_hint_ns)) {
@@ -585,9 +600,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
     TileWalker w;
     w.stride = tile_stride;
     EpiTile et{};
-    int tile = blockIdx.x;
+    int tile = kTileLookAhead ? 0 : first_tile_of(p);
     if constexpr (kTileLookAhead) {
-      w.seek(p, blockIdx.x, num_tiles);
+      w.seek(p, first_tile_of(p), num_tiles);
       if (w.tile < num_tiles) et = open_tile(w.ti);
       tile = w.tile;
     }
@@ -967,6 +982,10 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (p.m_valid != nullptr) num_m_blocks = min(num_m_blocks, ceil_div(max(__ldg(p.m_valid), 0), kBM));
   const int num_tiles = num_m_blocks * p.num_n_blocks;
   const int num_kb = ceil_div(p.K, kB16K);  // a ragged last block is zero-filled by TMA
+  // work items: (tile, K slice), the slices of a tile on neighbouring CTAs
+  const int splits = p.k_splits > 1 ? p.k_splits : 1;
+  const int kb_per = p.k_splits > 1 ? p.kb_per_split : num_kb;
+  const int num_items = num_tiles * splits;
   // dense form: no layout, every tile belongs to group 0
   auto tile_of = [&](int tile) {
     if (p.layout != nullptr) return get_tile(p, tile);
@@ -984,12 +1003,14 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const int tile = item / splits;
+      const int kb0 = (item - tile * splits) * kb_per, kb1 = min(kb0 + kb_per, num_kb);
       const TileInfo ti = tile_of(tile);
       if (!ti.valid) continue;
       const int a_row = ti.m_block * kBM;
       const int b_row = ti.g * p.N + ti.n_block * 256;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_hint_ns)) {
           if (lane == 0) report_timeout(p.status, kRoleProducer, tile, kb);
           ok = false;
@@ -1016,14 +1037,16 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a,
     int stage = 0, buf = 0;
     uint32_t phase = 0, bphase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const int tile = item / splits;
+      const int kb0 = (item - tile * splits) * kb_per, kb1 = min(kb0 + kb_per, num_kb);
       const TileInfo ti = tile_of(tile);
       if (!ti.valid) continue;
       if (!mbar_wait_bounded(tmem_empty_bar(buf), bphase ^ 1u, abort_flag, p.wait_hint_ns)) {
         if (lane == 0) report_timeout(p.status, kRoleMma, tile, -1);
         break;
       }
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, p.wait_hint_ns)) {
           if (lane == 0) report_timeout(p.status, kRoleMma, tile, kb);
           ok = false;
@@ -1039,10 +1062,10 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a,
           for (int k4 = 0; k4 < 4; ++k4) {
             // 16 bf16 = 32 bytes along K inside the 128-byte swizzle atom
             const uint64_t koff = (uint64_t)((k4 * 32) >> 4);
-            tc_mma_f16(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+            tc_mma_f16(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar(stage));
-          if (kb == num_kb - 1) tc_commit(tmem_full_bar(buf));  // the tile is complete
+          if (kb == kb1 - 1) tc_commit(tmem_full_bar(buf));  // the tile (or its K slice) is complete
         }
         __syncwarp();
         if (++stage == kSt) {
@@ -1063,7 +1086,9 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a,
     uint8_t* stage = stage_smem + h * kScatterWgBytes;
     int buf = 0;
     uint32_t bphase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const int tile = item / splits;
+      const int slice = item - tile * splits;
       const TileInfo ti = tile_of(tile);
       if (!ti.valid) continue;
       if (!mbar_wait_bounded(tmem_full_bar(buf), bphase, abort_flag, p.wait_hint_ns)) {
@@ -1079,7 +1104,8 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a,
         else row_ok = __ldg(p.layout + row) >= 0;
       }
       const uint32_t t0 = tmem_base + lane_addr + (uint32_t)buf * kUmmaN + (uint32_t)h * 128;
-      float* out_f32 = reinterpret_cast<float*>(p.out) + (size_t)row * p.N + col0;
+      float* out_f32 = reinterpret_cast<float*>(p.out) +
+                       ((size_t)slice * p.m_total + row) * p.N + col0;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
@@ -1217,9 +1243,16 @@ static uint32_t gemm_wait_hint_ns() {
   return (uint32_t)v;
 }
 
+// Tile-order tactic by the number of N blocks (sweep in launch_grouped_gemm).
+static int default_group_m(int num_n_blocks) {
+  return num_n_blocks >= 32 ? 16 : num_n_blocks >= 14 ? 8 : 1;
+}
+
+// keep_status: the status words are not cleared (a later launch of a chunked run must
+// not wipe what an earlier one reported).
 template <bool kSwiglu>
 static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, GemmParams p,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, bool keep_status = false) {
   if (p.m_total == 0) return kOk;
   CUtensorMap tm_a, tm_b0, tm_b1;
   int rc;
@@ -1243,7 +1276,7 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
     const char* e = getenv("MOEB_GEMM_GROUP_M");
     return e ? atoi(e) : 0;
   }();
-  p.group_m = group_env > 0 ? group_env : (p.num_n_blocks >= 32 ? 16 : p.num_n_blocks >= 14 ? 8 : 1);
+  p.group_m = group_env > 0 ? group_env : default_group_m(p.num_n_blocks);
   if (p.masked) p.group_m = 1;
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const GemmParams);
@@ -1284,7 +1317,8 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
   // per device and cheap, so it is simply repeated on every launch
   MOEB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      smem_bytes));
-  if (p.status) MOEB_CUDA_TRY(cudaMemsetAsync(p.status, 0, 4 * sizeof(int32_t), stream));
+  if (p.status && !keep_status && !status_scope_open())
+    MOEB_CUDA_TRY(cudaMemsetAsync(p.status, 0, 4 * sizeof(int32_t), stream));
   const long long tiles = (long long)p.num_m_blocks * p.num_n_blocks;
   // every CTA must be resident at once in the fused form (compute CTAs wait for
   // comm CTAs): one CTA per SM, never more CTAs than SMs
@@ -1475,6 +1509,109 @@ int moeb::fp8_mlp_overlapped(const void* A, const float* scale_a, const void* ga
   return kOk;
 }
 
+// Row ranges of a chunked MLP: plan[2c] = first row, plan[2c+1] = end row of chunk c.
+// The rows in use are split evenly into `chunks` ranges of whole groups of row blocks.
+__global__ void mlp_chunk_plan_kernel(const int32_t* __restrict__ m_valid, int chunks,
+                                      int align_rows, int32_t* __restrict__ plan) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int valid = max(m_valid[0], 0);
+  const int per = round_up(max(ceil_div(valid, chunks), 1), align_rows);
+  // (an empty chunk starts on the group boundary behind every row in use, so that its
+  // launch finds no tile at all)
+  const int valid_up = round_up(valid, align_rows);
+  for (int c = 0; c < chunks; ++c) {
+    plan[2 * c] = min(c * per, valid_up);
+    plan[2 * c + 1] = c + 1 == chunks ? valid : min((c + 1) * per, valid);
+  }
+}
+
+// Expert MLP of a rank in row chunks, for the expert-parallel layer: gate/up of chunk
+// c+1 (stream `main`, all SMs but n_down_ctas) runs beside the down projection of chunk
+// c (stream `aux`, n_down_ctas SMs), whose store warps send the rows home over NVLink.
+// The link, which bounds the down projection when most rows are remote, is then busy
+// from the end of the first gate/up chunk on instead of after the whole gate/up GEMM.
+// Unlike fp8_mlp_overlapped the kernels do not wait on one another: a chunk's down
+// launch follows its gate/up launch through an event, and both kernels keep the code
+// of the plain launches. The first gate/up chunk and the last down chunk have the GPU
+// to themselves. `plan` holds 2 * chunks int32 (written here); ev_chunk: one event per
+// chunk. The result is that of the two plain launches, bit for bit.
+int moeb::fp8_mlp_chunked(const void* A, const float* scale_a, const void* gate,
+                          const float* scale_gate, const void* up, const float* scale_up, void* D,
+                          float* scale_d, const void* down, const float* scale_down,
+                          const uint64_t* peer_out, size_t home_off, const int32_t* row_rank,
+                          const int32_t* row_pos, int m_total, const int32_t* m_valid_dev, int I,
+                          int H, int G, const int32_t* grouped_layout, int32_t* plan, int chunks,
+                          int n_down_ctas, int32_t* status_swiglu, int32_t* status_down,
+                          cudaStream_t main, cudaStream_t aux, cudaEvent_t ev_fork,
+                          cudaEvent_t ev_join, const cudaEvent_t* ev_chunk,
+                          cudaEvent_t ev_gate_up_done) {
+  int rc = check_common("fp8_mlp_chunked", A, scale_a, gate, scale_gate, D, m_total, I, H, G,
+                        MOEB_GEMM_M_GROUPED_CONTIGUOUS, grouped_layout, 0);
+  if (rc != kOk) return rc;
+  if (!up || !scale_up || !scale_d || !down || !scale_down || !peer_out || !row_rank || !row_pos ||
+      !plan || !m_valid_dev || !ev_chunk || chunks < 2 || chunks > 8 || n_down_ctas <= 0 ||
+      n_down_ctas >= sm_count() || !aligned16(up) || !aligned16(down)) {
+    set_last_error_msg("fp8_mlp_chunked: bad argument");
+    return kInvalidArgument;
+  }
+  if (m_total == 0) return kOk;
+  GemmParams g{};
+  g.scale_a = scale_a;
+  g.scale_b0 = scale_gate;
+  g.scale_b1 = scale_up;
+  g.out = D;
+  g.scale_d = scale_d;
+  g.layout = grouped_layout;
+  g.status = status_swiglu;
+  g.m_total = m_total;
+  g.N = I;
+  g.K = H;
+  g.G = G;
+  GemmParams d{};
+  d.scale_a = scale_d;
+  d.scale_b0 = scale_down;
+  d.scale_b1 = scale_down;
+  d.layout = grouped_layout;
+  d.status = status_down;
+  d.m_total = m_total;
+  d.N = H;
+  d.K = I;
+  d.G = G;
+  d.scatter_out = peer_out;
+  d.scatter_off = home_off;
+  d.scatter_rank = row_rank;
+  d.scatter_pos = row_pos;
+  // chunk boundaries on whole groups of row blocks of both kernels' tile orders
+  static const int group_env = [] {
+    const char* e = getenv("MOEB_GEMM_GROUP_M");
+    return e ? atoi(e) : 0;
+  }();
+  const int gm_a = group_env > 0 ? group_env : default_group_m(I / 128);
+  const int gm_b = group_env > 0 ? group_env : default_group_m(ceil_div(H, 256));
+  const int align_rows = kBM * (gm_a > gm_b ? gm_a : gm_b);
+  mlp_chunk_plan_kernel<<<1, 32, 0, main>>>(m_valid_dev, chunks, align_rows, plan);
+  MOEB_CUDA_TRY(cudaGetLastError());
+  MOEB_CUDA_TRY(cudaEventRecord(ev_fork, main));
+  MOEB_CUDA_TRY(cudaStreamWaitEvent(aux, ev_fork, 0));
+  const int all = sm_count();
+  for (int c = 0; c < chunks; ++c) {
+    g.m_begin = plan + 2 * c;
+    g.m_valid = plan + 2 * c + 1;
+    g.max_ctas = c == 0 ? 0 : all - n_down_ctas;
+    if ((rc = launch_grouped_gemm<true>(A, gate, up, g, main, c > 0)) != kOk) return rc;
+    MOEB_CUDA_TRY(cudaEventRecord(ev_chunk[c], main));
+    MOEB_CUDA_TRY(cudaStreamWaitEvent(aux, ev_chunk[c], 0));
+    d.m_begin = plan + 2 * c;
+    d.m_valid = plan + 2 * c + 1;
+    d.max_ctas = c + 1 == chunks ? 0 : n_down_ctas;
+    if ((rc = launch_grouped_gemm<false>(D, down, down, d, aux, c > 0)) != kOk) return rc;
+  }
+  if (ev_gate_up_done != nullptr) MOEB_CUDA_TRY(cudaEventRecord(ev_gate_up_done, main));
+  MOEB_CUDA_TRY(cudaEventRecord(ev_join, aux));
+  MOEB_CUDA_TRY(cudaStreamWaitEvent(main, ev_join, 0));
+  return kOk;
+}
+
 extern "C" int moeb_fp8_grouped_gemm_nt(const void* A, const float* scale_a, const void* W,
                                         const float* scale_w, void* out, int out_dtype,
                                         int m_total, int N, int K, int G, int gemm_type,
@@ -1559,6 +1696,54 @@ int moeb::fp8_gemm_nt_scatter_off(const void* A, const float* scale_a, const voi
   return launch_grouped_gemm<false>(A, W, W, p, stream);
 }
 
+// Dense D[s] = A[:, slice s of K] * B[:, slice s of K]^T, fp32 partial sums of k_splits K
+// slices at D + s * m_total * N (router.cu sums them). A [m_total, K], B [N, K] bf16.
+int moeb::bf16_gemm_splitk_f32(const void* A, const void* B, float* D, int m_total, int N, int K,
+                               int k_splits, int32_t* status_dev, cudaStream_t s) {
+  if (!A || !B || !D || m_total <= 0 || N <= 0 || K <= 0 || K % 8 != 0 || N % 4 != 0 ||
+      !aligned16(A) || !aligned16(B) || !aligned16(D) || k_splits < 1) {
+    set_last_error_msg("bf16_gemm_splitk_f32: bad argument");
+    return kInvalidArgument;
+  }
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  if ((rc = make_tile_map(&tm_a, A, (uint64_t)m_total, (uint64_t)K, 2)) != kOk) return rc;
+  if ((rc = make_tile_map(&tm_b, B, (uint64_t)N, (uint64_t)K, 2)) != kOk) return rc;
+  GemmParams p{};
+  p.out = D;
+  p.status = status_dev;
+  p.m_total = m_total;
+  p.N = N;
+  p.K = K;
+  p.G = 1;
+  p.out_f32 = 1;
+  p.wait_hint_ns = gemm_wait_hint_ns();
+  p.num_m_blocks = ceil_div(m_total, kBM);
+  p.num_n_blocks = ceil_div(N, 256);
+  const int num_kb = ceil_div(K, kB16K);
+  p.k_splits = bf16_splitk_slices(K, k_splits);
+  p.kb_per_split = ceil_div(num_kb, k_splits < num_kb ? k_splits : num_kb);
+  MOEB_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_bf16_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kGemmSmemBytesB16));
+  if (status_dev && !status_scope_open())
+    MOEB_CUDA_TRY(cudaMemsetAsync(status_dev, 0, 4 * sizeof(int32_t), s));
+  const long long items = (long long)p.num_m_blocks * p.num_n_blocks * p.k_splits;
+  const int grid = (int)(items < sm_count() ? items : sm_count());
+  grouped_gemm_bf16_kernel<<<grid, kGemmThreads, kGemmSmemBytesB16, s>>>(tm_a, tm_b, p);
+  MOEB_CUDA_TRY(cudaGetLastError());
+  return kOk;
+}
+
+// Slices a split into `want` parts really has: every slice holds at least one 64-element
+// K block.
+int moeb::bf16_splitk_slices(int K, int want) {
+  const int num_kb = ceil_div(K, kB16K);
+  if (want < 1) want = 1;
+  if (want > num_kb) want = num_kb;
+  return ceil_div(num_kb, ceil_div(num_kb, want));
+}
+
 extern "C" int moeb_bf16_gemm(const void* A, const void* B, void* D, int out_dtype, int m_total,
                               int N, int K, int G, int gemm_type, const int32_t* grouped_layout,
                               int max_m, int32_t* status_dev, void* stream) {
@@ -1608,7 +1793,8 @@ extern "C" int moeb_bf16_gemm(const void* A, const void* B, void* D, int out_dty
   MOEB_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_bf16_kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kGemmSmemBytesB16));
-  if (status_dev) MOEB_CUDA_TRY(cudaMemsetAsync(status_dev, 0, 4 * sizeof(int32_t), s));
+  if (status_dev && !status_scope_open())
+    MOEB_CUDA_TRY(cudaMemsetAsync(status_dev, 0, 4 * sizeof(int32_t), s));
   const long long tiles = (long long)p.num_m_blocks * p.num_n_blocks;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   grouped_gemm_bf16_kernel<<<grid, kGemmThreads, kGemmSmemBytesB16, s>>>(tm_a, tm_b, p);

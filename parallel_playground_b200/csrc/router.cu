@@ -230,6 +230,250 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
+// ------------------------------------------------------- logits, many experts --
+// More than 64 experts and many tokens: the kernel above would read x once per
+// 64-expert block. Here a warp owns 32 tokens x 128 experts of one K slice (two
+// m16 tiles that share every B fragment, 128 fp32 partial sums per thread), so a
+// CTA of 8 warps = (8 / KS) token tiles x KS slices covers 128 experts and x is
+// read once per 128-expert block: once from HBM and, with 256 experts, once more
+// from L2 by the CTA of the other block, which runs in the same wave. x goes from
+// global memory straight into the A fragments as above, one 64-element chunk per
+// slice ahead (32 KiB in flight per SM); W chunks [KS x 64 rows][128 experts] are
+// double-buffered in shared memory.
+constexpr int kKRW = 64;              // K elements per slice and chunk
+constexpr int kRtStepsW = kKRW / 32;
+constexpr int kWideNT8 = 16;          // 8-expert mma tiles per warp
+constexpr int kWideEP = 8 * kWideNT8; // experts per CTA
+
+__host__ __device__ constexpr int rt_wide_smem_bytes(int ks) {
+  const int wbuf = 2 * ks * kKRW * rt_ws(kWideNT8) * 2;
+  const int red = 8 * 32 * kWideEP * 4;
+  return wbuf > red ? wbuf : red;
+}
+
+template <int KS>
+__global__ void __launch_bounds__(kRtThreads, 1)
+router_logits_wide_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg,
+                          const float* __restrict__ bias, float* __restrict__ logits, int T, int H,
+                          int E) {
+  constexpr int TT = 8 / KS;
+  constexpr int EP = kWideEP;
+  constexpr int WS = rt_ws(kWideNT8);
+  constexpr int kBufElems = KS * kKRW * WS;
+  extern __shared__ __align__(16) uint8_t rt_smem[];
+  __nv_bfloat16* wsm = reinterpret_cast<__nv_bfloat16*>(rt_smem);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tm = warp % TT, ks = warp / TT;
+  const int e_base = blockIdx.y * EP;
+  const int t_tile = (blockIdx.x * TT + tm) * 32;
+  const int groups = ceil_div(H, 32);
+  const int slice_len = ceil_div(groups, KS) * 32;
+  const int num_chunks = ceil_div(slice_len, kKRW);
+  const int k_slice = ks * slice_len;
+  const bool vec_w = (E % 8) == 0;
+
+  // x rows of this thread: rows g and g+8 of both m16 tiles, clamped (rows past
+  // T are computed and dropped)
+  const int q = lane & 3;
+  const __nv_bfloat16* xr[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    xr[j] = x + (size_t)min(t_tile + (lane >> 2) + 8 * j, T - 1) * H + q * 8;
+
+  auto load_a = [&](uint4 (&f)[kRtStepsW][4], int chunk) {
+    const int k0 = k_slice + chunk * kKRW;
+#pragma unroll
+    for (int s = 0; s < kRtStepsW; ++s) {
+      const int k = k0 + s * 32;
+      const bool in = (chunk * kKRW + s * 32 < slice_len) && (k + q * 8 < H);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) f[s][j] = in ? ld_nc_v4(xr[j] + k) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  // W rows of every slice for one chunk -> buffer `buf`, each 32-row group in the
+  // order the mma consumes it (the permutation of the kernel above)
+  auto stage_w = [&](int chunk, int buf) {
+    __nv_bfloat16* dst = wsm + buf * kBufElems;
+    for (int v = threadIdx.x; v < KS * kKRW * kWideNT8; v += kRtThreads) {
+      const int row = v / kWideNT8, nv = v % kWideNT8;
+      const int sl = row / kKRW, r = row % kKRW;
+      const int h = sl * slice_len + chunk * kKRW + r;
+      const int e = e_base + nv * 8;
+      const bool row_in = (chunk * kKRW + r < slice_len) && h < H;
+      const int p = r & 31;
+      const int pos = 16 * ((p >> 2) & 1) + 8 * ((p >> 1) & 1) + 2 * (p >> 3) + (p & 1);
+      __nv_bfloat16* d = dst + (row - p + pos) * WS + nv * 8;
+      if (vec_w) {
+        const bool in = row_in && e < E;
+        cp_async_16(smem_u32(d), in ? (const void*)(wg + (size_t)h * E + e) : (const void*)wg,
+                    in ? 16 : 0);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          d[i] = (row_in && e + i < E) ? wg[(size_t)h * E + e + i] : __float2bfloat16(0.0f);
+      }
+    }
+    cp_async_commit_group();
+  };
+
+  float acc[2][kWideNT8][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int i = 0; i < kWideNT8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[m][i][j] = 0.0f;
+
+  const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8;
+  const int lm_col = (lane >> 4) * 8;
+
+  uint4 f0[kRtStepsW][4], f1[kRtStepsW][4];
+  stage_w(0, 0);
+  load_a(f0, 0);
+
+  auto compute = [&](const uint4 (&f)[kRtStepsW][4], int buf) {
+    const uint32_t wbase = smem_u32(wsm + buf * kBufElems + (ks * kKRW) * WS);
+#pragma unroll
+    for (int s = 0; s < kRtStepsW; ++s) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t a[2][4];
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          const uint4 fa = f[s][2 * m], fb = f[s][2 * m + 1];
+          a[m][0] = half ? fa.z : fa.x;
+          a[m][2] = half ? fa.w : fa.y;
+          a[m][1] = half ? fb.z : fb.x;
+          a[m][3] = half ? fb.w : fb.y;
+        }
+        const uint32_t row_addr = wbase + (uint32_t)((s * 32 + half * 16 + lm_row) * WS) * 2u;
+#pragma unroll
+        for (int j = 0; j < kWideNT8 / 2; ++j) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, row_addr + (uint32_t)(j * 16 + lm_col) * 2u);
+#pragma unroll
+          for (int m = 0; m < 2; ++m) {
+            mma_bf16_16816(acc[m][2 * j], a[m][0], a[m][1], a[m][2], a[m][3], b[0], b[1]);
+            mma_bf16_16816(acc[m][2 * j + 1], a[m][0], a[m][1], a[m][2], a[m][3], b[2], b[3]);
+          }
+        }
+      }
+    }
+  };
+
+  for (int c = 0; c < num_chunks; c += 2) {
+    cp_async_wait_all();
+    __syncthreads();
+    if (c + 1 < num_chunks) {
+      stage_w(c + 1, 1);
+      load_a(f1, c + 1);
+    }
+    compute(f0, 0);
+    if (c + 1 >= num_chunks) break;
+    cp_async_wait_all();
+    __syncthreads();
+    if (c + 2 < num_chunks) {
+      stage_w(c + 2, 0);
+      load_a(f0, c + 2);
+    }
+    compute(f1, 1);
+  }
+  __syncthreads();  // the W buffers become the partial sums [ks][tm][32 rows][EP]
+
+  float* red = reinterpret_cast<float*>(rt_smem);
+  {
+    float* mine = red + (size_t)(ks * TT + tm) * 32 * EP;
+    const int r = lane >> 2, cpair = (lane & 3) * 2;
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int i = 0; i < kWideNT8; ++i) {
+        float* o = mine + (16 * m + r) * EP + i * 8 + cpair;
+        o[0] = acc[m][i][0];
+        o[1] = acc[m][i][1];
+        o[8 * EP] = acc[m][i][2];
+        o[8 * EP + 1] = acc[m][i][3];
+      }
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < TT * 32 * EP; o += kRtThreads) {
+    const int e_in = o % EP, row = (o / EP) % 32, m = o / (EP * 32);
+    const int t = (blockIdx.x * TT + m) * 32 + row, e = e_base + e_in;
+    if (t >= T || e >= E) continue;
+    float v = red[(size_t)m * 32 * EP + row * EP + e_in];
+#pragma unroll
+    for (int sl = 1; sl < KS; ++sl) v += red[(size_t)(sl * TT + m) * 32 * EP + row * EP + e_in];
+    logits[(size_t)t * E + e] = v + (bias != nullptr ? bias[e] : 0.0f);
+  }
+}
+
+// ------------------------------------------- logits on the tcgen05 tensor cores --
+// With more than 64 experts the contraction itself bounds the mma.sync kernels above
+// (measured on B200, 8192 tokens x 4096 x 256 experts: 104 us, ~165 TFLOP/s, against
+// 12 us for reading x once). Given a workspace the logits go through the tcgen05 bf16
+// GEMM instead: W [H,E] is transposed to K-major [E,H] (a few MB), the GEMM runs with
+// the K range split over enough CTAs to fill the GPU, and the slices' fp32 partial sums
+// are added in slice order (+ bias) - the same result on every run.
+__global__ void __launch_bounds__(256)
+router_transpose_w_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt,
+                          int H, int E) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  const int h0 = blockIdx.x * 32, e0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int h = h0 + ty + 8 * i, e = e0 + tx;
+    tile[ty + 8 * i][tx] = (h < H && e < E) ? w[(size_t)h * E + e] : __float2bfloat16(0.0f);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int e = e0 + ty + 8 * i, h = h0 + tx;
+    if (e < E && h < H) wt[(size_t)e * H + h] = tile[tx][ty + 8 * i];
+  }
+}
+
+__global__ void __launch_bounds__(256)
+router_sum_slices_kernel(const float* __restrict__ partial, const float* __restrict__ bias,
+                         float* __restrict__ logits, size_t n, int E, int slices) {
+  // n = T * E, a multiple of 4 (E % 8 == 0)
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n;
+       i += (size_t)gridDim.x * blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(partial + i);
+    for (int s = 1; s < slices; ++s) {
+      const float4 o = *reinterpret_cast<const float4*>(partial + (size_t)s * n + i);
+      v.x += o.x;
+      v.y += o.y;
+      v.z += o.z;
+      v.w += o.w;
+    }
+    if (bias != nullptr) {
+      const int e = (int)(i % (size_t)E);
+      v.x += bias[e];
+      v.y += bias[e + 1];
+      v.z += bias[e + 2];
+      v.w += bias[e + 3];
+    }
+    *reinterpret_cast<float4*>(logits + i) = v;
+  }
+}
+
+// K slices of the tensor-core path, 0 = the path does not apply to this shape.
+static int tc_router_slices(int T, int H, int E) {
+  if (E <= 64 || E % 8 != 0 || T < 1024) return 0;
+  const long long tiles = (long long)ceil_div(T, 128) * ceil_div(E, 256);
+  int want = (int)(148 / tiles);
+  if (want < 1) want = 1;
+  if (want > 8) want = 8;
+  // at least 8 K blocks of 64 per slice
+  while (want > 1 && ceil_div(H, 64) / want < 8) --want;
+  return bf16_splitk_slices(H, want);
+}
+static size_t tc_router_wt_bytes(int H, int E) {
+  return ((size_t)E * H * 2 + 255) / 256 * 256;
+}
+
 // ------------------------------------------------------------------ select --
 // One warp per token; the token's scores live in shared memory. All arithmetic
 // that decides an index or a weight goes through det_math.h so that the CPU
@@ -389,6 +633,30 @@ static cudaError_t launch_logits(const void* x, const void* wg, const float* bia
   return cudaGetLastError();
 }
 
+template <int KS>
+static cudaError_t launch_logits_wide(const void* x, const void* wg, const float* bias,
+                                      float* logits, int T, int H, int E, cudaStream_t s) {
+  constexpr int smem = rt_wide_smem_bytes(KS);
+  auto kernel = router_logits_wide_kernel<KS>;
+  cudaError_t err =
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err != cudaSuccess) return err;
+  const dim3 grid(ceil_div(T, 32 * (8 / KS)), ceil_div(E, kWideEP));
+  kernel<<<grid, kRtThreads, smem, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)wg, bias,
+                                        logits, T, H, E);
+  return cudaGetLastError();
+}
+
+// K slices of the many-expert kernel, 0 = use the kernel with 64-expert blocks:
+// the most tokens per CTA (fewest passes over W) that still fills most of the SMs.
+static int pick_wide_slices(int T, int E) {
+  if (E <= 64) return 0;
+  const long long blocks = ceil_div(E, kWideEP);
+  if ((long long)ceil_div(T, 128) * blocks >= 96) return 2;
+  if ((long long)ceil_div(T, 64) * blocks >= 96) return 4;
+  return 0;
+}
+
 // Tile shape. Many tokens: 64 tokens x 2 K slices per CTA with up to 64 experts,
 // so that x is read once (or once per 64-expert block, from L2). Few tokens
 // (decode): 16 tokens x 8 K slices per CTA and expert blocks narrow enough to
@@ -420,8 +688,13 @@ extern "C" int moeb_router_logits(const void* x_bf16, const void* w_gate_bf16,
   if (T == 0) return kOk;
   cudaStream_t s = (cudaStream_t)stream;
   const RouterTile tile = pick_router_tile(T, E);
+  const int wide = pick_wide_slices(T, E);
   cudaError_t err = cudaSuccess;
-  if (tile.ks == 2) {
+  if (wide == 2) {
+    err = launch_logits_wide<2>(x_bf16, w_gate_bf16, logit_bias, logits, T, H, E, s);
+  } else if (wide == 4) {
+    err = launch_logits_wide<4>(x_bf16, w_gate_bf16, logit_bias, logits, T, H, E, s);
+  } else if (tile.ks == 2) {
     switch (tile.nt8) {
       case 8: err = launch_logits<8, 2>(x_bf16, w_gate_bf16, logit_bias, logits, T, H, E, s); break;
       case 4: err = launch_logits<4, 2>(x_bf16, w_gate_bf16, logit_bias, logits, T, H, E, s); break;
@@ -434,6 +707,50 @@ extern "C" int moeb_router_logits(const void* x_bf16, const void* w_gate_bf16,
   }
   MOEB_CUDA_TRY(err);
   MOEB_CUDA_TRY(cudaGetLastError());
+  return kOk;
+}
+
+extern "C" size_t moeb_router_logits_workspace_bytes(int T, int H, int E) {
+  using namespace moeb;
+  if (T <= 0 || H <= 0 || E <= 0 || H % 8 != 0) return 0;
+  if (tc_router_slices(T, H, E) == 0) return 0;
+  // slices * T <= max(T, 148 * 128) (a split never makes more items than SMs), so this
+  // size also serves every smaller token count: a workspace sized for the most tokens
+  // a caller will ever pass is enough for all its calls
+  const size_t rows = T > 148 * 128 ? (size_t)T : (size_t)148 * 128;
+  return tc_router_wt_bytes(H, E) + rows * E * 4;
+}
+
+extern "C" int moeb_router_logits_ws(const void* x_bf16, const void* w_gate_bf16,
+                                     const float* logit_bias, float* logits, int T, int H, int E,
+                                     void* workspace, size_t workspace_bytes, int32_t* status_dev,
+                                     void* stream) {
+  using namespace moeb;
+  const size_t need = moeb_router_logits_workspace_bytes(T, H, E);
+  if (need == 0 || !workspace || workspace_bytes < need ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    return moeb_router_logits(x_bf16, w_gate_bf16, logit_bias, logits, T, H, E, stream);
+  if (!x_bf16 || !w_gate_bf16 || !logits ||
+      ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(logits)) & 15u) != 0) {
+    set_last_error_msg("moeb_router_logits_ws: null or unaligned pointer (x, logits: 16 bytes)");
+    return kInvalidArgument;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const int slices = tc_router_slices(T, H, E);
+  __nv_bfloat16* wt = static_cast<__nv_bfloat16*>(workspace);
+  float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + tc_router_wt_bytes(H, E));
+  router_transpose_w_kernel<<<dim3(ceil_div(H, 32), ceil_div(E, 32)), 256, 0, s>>>(
+      (const __nv_bfloat16*)w_gate_bf16, wt, H, E);
+  MOEB_CUDA_TRY(cudaGetLastError());
+  const bool direct = slices == 1 && logit_bias == nullptr;
+  int rc = bf16_gemm_splitk_f32(x_bf16, wt, direct ? logits : partial, T, E, H, slices, status_dev, s);
+  if (rc != kOk) return rc;
+  if (!direct) {
+    const size_t n = (size_t)T * E;
+    const int blocks = (int)((n / 4 + 255) / 256 < 148 * 8 ? (n / 4 + 255) / 256 : 148 * 8);
+    router_sum_slices_kernel<<<blocks, 256, 0, s>>>(partial, logit_bias, logits, n, E, slices);
+    MOEB_CUDA_TRY(cudaGetLastError());
+  }
   return kOk;
 }
 

@@ -75,7 +75,8 @@ def _need_cuda(*tensors: torch.Tensor) -> None:
 
 def status_word(device: torch.device | int | None = None) -> torch.Tensor:
     """int32[12] device word that kernels fill when a bounded wait expires:
-    [0:4] gate/up GEMM, [4:8] down GEMM (each zeroed by its launch), [8:12] the
+    [0:4] gate/up GEMM (and what runs before it in a layer call: the router's GEMM, the
+    dispatch), [4:8] down GEMM (each zeroed by the call that uses it), [8:12] the
     expert-parallel rank barrier (never zeroed: the first expiry sticks)."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index
     if dev not in _status_words:
@@ -317,7 +318,15 @@ def fused_silu_mul_quant(gemm_out, swiglu_out, scale) -> None:
 
 
 # ---------------------------------------------------------- a1, a2, a4, a7 --
-def router_logits(x, w_gate, logits, bias=None) -> None:
+def router_logits_workspace_bytes(T: int, H: int, E: int) -> int:
+    """Scratch bytes with which router_logits runs on the tcgen05 tensor cores (many
+    tokens, more than 64 experts); 0 where that path does not apply."""
+    return int(cabi.load().moeb_router_logits_workspace_bytes(int(T), int(H), int(E)))
+
+
+def router_logits(x, w_gate, logits, bias=None, workspace=None) -> None:
+    """logits = x @ w_gate (+ bias). `workspace`: optional uint8 device tensor of
+    router_logits_workspace_bytes(T, H, E) bytes (see there)."""
     _need_cuda(x, w_gate, logits, bias)
     T, H = x.shape
     E = w_gate.shape[1]
@@ -326,6 +335,12 @@ def router_logits(x, w_gate, logits, bias=None) -> None:
         raise ValueError("router_logits: x [T,H] bf16, w_gate [H,E] bf16, logits [T,E] fp32")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != E):
         raise ValueError("router bias must be float32 [E]")
+    if workspace is not None:
+        _need_cuda(workspace)
+        cabi.call("moeb_router_logits_ws", _ptr(x), _ptr(w_gate), _ptr(bias), _ptr(logits), T, H, E,
+                  _ptr(workspace), workspace.numel() * workspace.element_size(),
+                  status_word(x.device).data_ptr(), _stream())
+        return
     cabi.call("moeb_router_logits", _ptr(x), _ptr(w_gate), _ptr(bias), _ptr(logits), T, H, E,
               _stream())
 

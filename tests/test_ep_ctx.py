@@ -71,19 +71,26 @@ def _worker(rank, world, port, q):
         layer = lambda out, fused, x=d.x: ctx.moe_forward(  # noqa: E731
             x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale, d.down, d.down_scale, out,
             shape, fused=fused)
-        # the two expert GEMMs side by side on disjoint SMs (an option; the default runs
-        # them one after the other): same bits
-        os.environ["MOEB_EP_DOWN_SMS"] = "40"
-        other_mlp = EPContext(T, shape.E, k, H, device=rank)
-        os.environ.pop("MOEB_EP_DOWN_SMS")
-        for _ in range(2):
-            out = torch.full((T, H), 8.0, dtype=torch.bfloat16, device=dev)
-            other_mlp.moe_forward(d.x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale,
-                                  d.down, d.down_scale, out, shape, fused=False)
-            torch.cuda.synchronize()
-            mc.check_device_status()
-            assert torch.equal(bits(out), bits(out_ref))
-        other_mlp.close()
+        # the other ways to run the two expert GEMMs of the whole-layer call: one after the
+        # other, in row chunks (the down projection of a chunk beside the gate/up GEMM of
+        # the next), as two whole kernels side by side. Same bits every time.
+        assert ctx.mlp_mode == ("chunks" if world > 1 else "seq")
+        for mode, extra in (("seq", {}), ("chunks", {"MOEB_EP_MLP_CHUNKS": "3"}),
+                            ("chunks", {"MOEB_EP_MLP_CHUNKS": "8", "MOEB_EP_DOWN_SMS": "30"}),
+                            ("beside", {"MOEB_EP_DOWN_SMS": "40"})):
+            os.environ.update(MOEB_EP_MLP=mode, **extra)
+            other_mlp = EPContext(T, shape.E, k, H, device=rank)
+            for key in ("MOEB_EP_MLP", *extra):
+                os.environ.pop(key)
+            assert other_mlp.mlp_mode == mode
+            for _ in range(2):
+                out = torch.full((T, H), 8.0, dtype=torch.bfloat16, device=dev)
+                other_mlp.moe_forward(d.x, d.w_router, None, d.gate, d.gate_scale, d.up,
+                                      d.up_scale, d.down, d.down_scale, out, shape, fused=False)
+                torch.cuda.synchronize()
+                mc.check_device_status()
+                assert torch.equal(bits(out), bits(out_ref)), (mode, extra)
+            other_mlp.close()
         pull_ctx = EPContext(T, shape.E, k, H, device=rank, transport="pull")
         for fused in (False, True, True, False, "pull", True, "pull"):   # buffers alternate by step
             out = torch.full((T, H), 9.0, dtype=torch.bfloat16, device=dev)

@@ -61,7 +61,12 @@ def test_router_select_bit_exact(mc, oracle_mod, T, E, k, mode, n_group, topk_gr
                                         (33, 7168, 256, False), (64, 512, 24, True),
                                         (50, 520, 20, True), (8192, 4096, 32, False),
                                         (130, 7168, 256, True), (6200, 2048, 128, False),
-                                        (7000, 776, 12, True), (1, 8, 1, False)])
+                                        (7000, 776, 12, True), (1, 8, 1, False),
+                                        # many tokens and more than 64 experts: the kernel with
+                                        # 128-expert blocks (ragged token, K and expert edges)
+                                        (8192, 4096, 256, True), (4096, 7168, 256, False),
+                                        (4100, 1032, 136, True), (6500, 520, 100, True),
+                                        (12300, 264, 72, False)])
 def test_router_logits(mc, oracle_mod, T, H, E, bias):
     g = torch.Generator().manual_seed(5)
     x = torch.randn(T, H, generator=g).bfloat16()
@@ -72,6 +77,39 @@ def test_router_logits(mc, oracle_mod, T, H, E, bias):
     mc.router_logits(x.to(DEV), wg.to(DEV), out, None if b is None else b.to(DEV))
     # fp32 accumulation in a different order: |err| <= 1e-4 * (1 + |ref|)
     assert np.all(np.abs(out.cpu().numpy() - ref) <= 1e-4 * (1 + np.abs(ref)))
+
+
+@pytest.mark.parametrize("T,H,E,bias", [(8192, 4096, 256, True), (4096, 7168, 256, False),
+                                        (4100, 1032, 136, True), (1024, 2048, 128, False),
+                                        (20000, 520, 72, True), (2000, 8200, 1024, False)])
+def test_router_logits_tensor_core_path(mc, oracle_mod, T, H, E, bias):
+    """With a workspace, many tokens and more than 64 experts the logits come from the
+    tcgen05 bf16 GEMM (transposed gate matrix, K split over the SMs, slices summed in a
+    fixed order): same tolerance against the oracle, same bits on every run, and the
+    workspace is all the call writes besides the logits."""
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    wg = (torch.randn(H, E, generator=g) * 0.02).bfloat16()
+    b = torch.randn(E, generator=g) if bias else None
+    ref = oracle_mod.router_logits(x, wg, b)
+    need = mc.router_logits_workspace_bytes(T, H, E)
+    assert need > 0
+    assert mc.router_logits_workspace_bytes(T // 2, H, E) <= need   # serves fewer tokens too
+    ws = torch.empty(need + 512, dtype=torch.uint8, device=DEV)
+    ws[need:].fill_(0x5a)
+    xd, wd, bd = x.to(DEV), wg.to(DEV), None if b is None else b.to(DEV)
+    outs = []
+    for _ in range(2):
+        out = torch.full((T, E), 7.0, dtype=torch.float32, device=DEV)
+        mc.router_logits(xd, wd, out, bd, workspace=ws[:need])
+        mc.check_device_status()
+        outs.append(out.cpu().numpy())
+    assert np.all(np.abs(outs[0] - ref) <= 1e-4 * (1 + np.abs(ref)))
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    assert bool((ws[need:] == 0x5a).all())
+    # shapes the path does not cover fall back to the plain kernels
+    assert mc.router_logits_workspace_bytes(512, H, E) == 0
+    assert mc.router_logits_workspace_bytes(T, H, 32) == 0
 
 
 # -------------------------------------------------------------------- plan --
@@ -734,10 +772,11 @@ def test_full_size_gemm_linearity_and_sampled_rows(mc, oracle_mod):
     sd = torch.zeros((I // 128, M), dtype=torch.float32, device=DEV)
     mc.fp8_grouped_gemm_swiglu(ex, es, inp.gate, inp.gate_scale, inp.up, inp.up_scale, D, sd,
                                mc.GemmType.MGroupedContiguous, plan.grouped_layout)
-    y = torch.empty((M, H), dtype=torch.float32, device=DEV)
+    # (row blocks behind the last expert are not visited: zeros, not whatever memory held)
+    y = torch.zeros((M, H), dtype=torch.float32, device=DEV)
     mc.fp8_grouped_gemm_nt(D, sd, inp.down, inp.down_scale, y, mc.GemmType.MGroupedContiguous,
                            plan.grouped_layout)
-    y2 = torch.empty((M, H), dtype=torch.float32, device=DEV)
+    y2 = torch.zeros((M, H), dtype=torch.float32, device=DEV)
     mc.fp8_grouped_gemm_nt(D, sd * 2, inp.down, inp.down_scale, y2, mc.GemmType.MGroupedContiguous,
                            plan.grouped_layout)
     mc.check_device_status()

@@ -724,14 +724,17 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
   c->ev_fork = c->ev_join = nullptr;
   // How the whole-layer call runs the two expert GEMMs (MOEB_EP_MLP = seq | chunks |
   // beside). With more than one rank the down projection is bound by NVLink (most of
-  // its rows go to other ranks) and the link idles during gate/up. "chunks" (default
-  // for W > 1) splits the rows into MOEB_EP_MLP_CHUNKS ranges and runs the down
-  // projection of a range, on MOEB_EP_DOWN_SMS SMs, beside the gate/up GEMM of the next
-  // one. "beside" runs two whole kernels side by side, the down kernel waiting per row
-  // block for the gate/up kernel; measured at 4 ranks on the default workload it is no
-  // faster than "seq" (1.62 against 1.57 ms: its gate/up kernel carries a store warp
-  // that costs what the overlap wins).
-  c->mlp_mode = cfg->world > 1 ? 1 : 0;
+  // its rows go to other ranks) and the link idles during gate/up. "chunks" splits the
+  // rows into MOEB_EP_MLP_CHUNKS ranges and runs the down projection of a range, on
+  // MOEB_EP_DOWN_SMS SMs, beside the gate/up GEMM of the next one. "beside" runs two
+  // whole kernels side by side, the down kernel waiting per row block for the gate/up
+  // kernel. Measured at 4 ranks (both GEMMs, ms): default workload seq 1.59, chunks
+  // 1.53 (4 ranges, 52 SMs; 6 ranges 1.59, 44 SMs 1.70), beside 1.62; DeepSeek-V3
+  // shape seq 1.86, chunks 1.89. What the overlap wins (the SM time the down kernel
+  // spends waiting for the link, at most 0.2 ms) goes into eight launches' ramps and
+  // tails (chunks) or into the store warp the gate/up kernel then carries (beside), so
+  // the default stays "seq" and the other two are options.
+  c->mlp_mode = 0;
   if (const char* o = getenv("MOEB_EP_MLP")) {
     if (!strcmp(o, "seq") || !strcmp(o, "0")) c->mlp_mode = 0;
     else if (!strcmp(o, "chunks")) c->mlp_mode = 1;

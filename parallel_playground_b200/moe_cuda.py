@@ -324,10 +324,25 @@ def router_logits_workspace_bytes(T: int, H: int, E: int) -> int:
     return int(cabi.load().moeb_router_logits_workspace_bytes(int(T), int(H), int(E)))
 
 
+_router_scratch: dict = {}
+
+
 def router_logits(x, w_gate, logits, bias=None, workspace=None) -> None:
-    """logits = x @ w_gate (+ bias). `workspace`: optional uint8 device tensor of
-    router_logits_workspace_bytes(T, H, E) bytes (see there)."""
+    """logits = x @ w_gate (+ bias). `workspace`: uint8 device tensor of
+    router_logits_workspace_bytes(T, H, E) bytes; None: a scratch tensor kept per device
+    (so that every caller of this module gets the same kernels, and the same bits, as the
+    whole-layer calls of the library, which always bring a workspace); False: none, the
+    plain kernels."""
     _need_cuda(x, w_gate, logits, bias)
+    if workspace is None:
+        need = router_logits_workspace_bytes(x.shape[0], x.shape[1], w_gate.shape[1])
+        if need > 0:
+            key = x.device.index
+            if key not in _router_scratch or _router_scratch[key].numel() < need:
+                _router_scratch[key] = torch.empty(need, dtype=torch.uint8, device=x.device)
+            workspace = _router_scratch[key]
+    elif workspace is False:
+        workspace = None
     T, H = x.shape
     E = w_gate.shape[1]
     if w_gate.shape[0] != H or x.dtype != torch.bfloat16 or w_gate.dtype != torch.bfloat16 \

@@ -74,7 +74,7 @@ def _worker(rank, world, port, q):
         # the other ways to run the two expert GEMMs of the whole-layer call: one after the
         # other, in row chunks (the down projection of a chunk beside the gate/up GEMM of
         # the next), as two whole kernels side by side. Same bits every time.
-        assert ctx.mlp_mode == ("chunks" if world > 1 else "seq")
+        assert ctx.mlp_mode == "seq"
         for mode, extra in (("seq", {}), ("chunks", {"MOEB_EP_MLP_CHUNKS": "3"}),
                             ("chunks", {"MOEB_EP_MLP_CHUNKS": "8", "MOEB_EP_DOWN_SMS": "30"}),
                             ("beside", {"MOEB_EP_DOWN_SMS": "40"})):

@@ -73,8 +73,10 @@ def test_router_logits(mc, oracle_mod, T, H, E, bias):
     wg = (torch.randn(H, E, generator=g) * 0.02).bfloat16()
     b = torch.randn(E, generator=g) if bias else None
     ref = oracle_mod.router_logits(x, wg, b)
+    # (workspace=False: the kernels that need no scratch memory; the tensor-core path has
+    # its own test below)
     out = torch.empty((T, E), dtype=torch.float32, device=DEV)
-    mc.router_logits(x.to(DEV), wg.to(DEV), out, None if b is None else b.to(DEV))
+    mc.router_logits(x.to(DEV), wg.to(DEV), out, None if b is None else b.to(DEV), workspace=False)
     # fp32 accumulation in a different order: |err| <= 1e-4 * (1 + |ref|)
     assert np.all(np.abs(out.cpu().numpy() - ref) <= 1e-4 * (1 + np.abs(ref)))
 
@@ -107,6 +109,10 @@ def test_router_logits_tensor_core_path(mc, oracle_mod, T, H, E, bias):
     assert np.all(np.abs(outs[0] - ref) <= 1e-4 * (1 + np.abs(ref)))
     assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
     assert bool((ws[need:] == 0x5a).all())
+    # the module's own scratch tensor (no workspace argument) gives the same bits
+    out = torch.empty((T, E), dtype=torch.float32, device=DEV)
+    mc.router_logits(xd, wd, out, bd)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), outs[0].view(np.uint32))
     # shapes the path does not cover fall back to the plain kernels
     assert mc.router_logits_workspace_bytes(512, H, E) == 0
     assert mc.router_logits_workspace_bytes(T, H, 32) == 0

@@ -36,6 +36,16 @@ from parallel_playground_b200 import workloads as wl  # noqa: E402
 KERNELS_PER_STEP_1GPU = 9  # logits, select, plan x3, permute_quant, gate/up GEMM, down GEMM, combine
 
 
+def router_extra_launches(mc, shape, has_bias):
+    """The logits of a wide router (many tokens, more than 64 experts) take three launches
+    instead of one: gate-matrix transpose, tcgen05 GEMM with split K, slice sum (the sum is
+    left out when one slice without a bias writes the logits itself)."""
+    if mc.router_logits_workspace_bytes(shape.T, shape.H, shape.E) == 0:
+        return 0
+    tiles = -(-shape.T // 128) * -(-shape.E // 256)
+    return 2 if (148 // tiles > 1 or has_bias) else 1
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -441,6 +451,7 @@ def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused, mode="auto"
     chunks = int(os.environ.get("MOEB_EP_MLP_CHUNKS", "4"))
     # chunked: one plan kernel and two GEMM launches per chunk instead of two launches
     extra = 2 * chunks - 1 if mlp_mode == "chunks" else 0
+    extra += router_extra_launches(mc, shape, bias_d is not None)
     layer = {"kernels_per_step": (14 if push else (15 if fused else 16)) + extra, "out": out,
              "ctx": ctx, "mlp_mode": mlp_mode, "mlp_chunks": chunks if mlp_mode == "chunks" else 0,
              "mlp_overlapped": overlapped, "down_sms": down_sms if overlapped else 0,
@@ -874,8 +885,9 @@ def build_single_gpu_step(mc, shape, d, bias_d, dev):
             events["down"].append((b, c))
         mc.unpermute_combine(ey, plan.dst_row, wts, out)
 
-    layer = {"kernels_per_step": KERNELS_PER_STEP_1GPU, "out": out,
-             "routed_rows": lambda: int(plan.expert_counts.sum().item())}
+    layer = {"kernels_per_step": KERNELS_PER_STEP_1GPU + router_extra_launches(mc, shape,
+                                                                              bias_d is not None),
+             "out": out, "routed_rows": lambda: int(plan.expert_counts.sum().item())}
     return step, events, layer
 
 

@@ -205,14 +205,24 @@ def nvlink_bytes(gpu_index):
 
 
 # ------------------------------------------------------------------ CPU arm --
+def dequantised_weights_fit_host(shape):
+    """fp32 copies of all experts' three matrices within half of the free host memory?"""
+    need = 3.0 * shape.E * shape.H * shape.I * 4
+    try:
+        import psutil
+        return need <= 0.5 * psutil.virtual_memory().available
+    except Exception:  # noqa: BLE001 - no psutil: stay on the small side
+        return shape.E <= 64
+
+
 def cpu_reference_arm(shape, sample_tokens, steps, warmup, world=1):
     """Times the oracle (a CPU restatement of the reference path, fp32 on the
     de-quantised FP8 weights, torch CPU matmul on every host core) on a bounded
-    sample of the workload's tokens, all `shape.E` experts present. Up to 64
-    experts the weights are de-quantised beforehand (preparation, not timed, like
-    the GPU arm's pre-quantised weights); beyond that the fp32 copies would not fit
-    the host and each expert is de-quantised when its rows are processed, inside
-    the timed region."""
+    sample of the workload's tokens, all `shape.E` experts present. The weights
+    are de-quantised beforehand (preparation, not timed, like the GPU arm's
+    pre-quantised weights) where their fp32 copies fit the host's free memory
+    (19 GB for 256 experts of the default shape); otherwise each expert is
+    de-quantised when its rows are processed, inside the timed region."""
     import numpy as np
     import oracle
     torch.set_num_threads(os.cpu_count() or 1)
@@ -225,7 +235,7 @@ def cpu_reference_arm(shape, sample_tokens, steps, warmup, world=1):
     if bias is None and shape.zipf_bias > 0:
         bias = wl.zipf_log_bias(shape.E, shape.zipf_bias)
     q = lambda t: t.view(torch.uint8).numpy()  # noqa: E731
-    keep_f32 = shape.E <= 64
+    keep_f32 = dequantised_weights_fit_host(shape)
     experts = []
     for e in range(shape.E):
         w = wl.make_expert_weights(shape, e)
@@ -279,8 +289,13 @@ def run_reference(args):
         return 0
     world = max(1, args.gpus)
     shape = bench_shape(args, world)
-    steps = max(1, min(args.steps, 3 if world == 1 else 1))
-    warm = 1 if (args.warmup > 0 and world == 1) else 0
+    # K timed passes after W warm-up passes over the bounded sample (about a second each);
+    # only where the weights must be de-quantised inside every pass (tens of seconds) the
+    # run is cut to one pass so that it still ends within minutes
+    if dequantised_weights_fit_host(shape):
+        steps, warm = max(1, args.steps), max(0, args.warmup)
+    else:
+        steps, warm = 1, 0
     cb = cpu_reference_arm(shape, args.cpu_sample_tokens, steps, warm, world)
     line = {
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": cb["value"],

@@ -459,7 +459,7 @@ def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused, mode="auto"
     # pull: cast, mark, announce, pull (or inside the GEMM), pos; gate/up GEMM, down GEMM,
     # barrier, reduce
     # how the library runs the two expert GEMMs of the whole-layer call: one after the
-    # other, or overlapped (row chunks / two kernels side by side, see moeb_ep_mlp_mode)
+    # other, or overlapped in row chunks (see moeb_ep_mlp_mode)
     mlp_mode = "seq" if fused else ctx.mlp_mode
     overlapped = mlp_mode != "seq"
     down_sms = int(os.environ.get("MOEB_EP_DOWN_SMS", "52"))
@@ -559,10 +559,10 @@ def gemm_figures(shape, world, rows, st, peaks, fp8, overlapped=False, down_sms=
         return r
 
     if overlapped:
-        # expert parallel: the two GEMMs run at the same time on disjoint SMs (in row
-        # chunks, or as two kernels with the down kernel following row block by row block;
-        # the down rows feed NVLink meanwhile); only their common span is meaningful:
-        # swiglu = up to the end of gate/up, down = what is left of the down projection
+        # expert parallel, chunked MLP: the down projection of a row chunk runs beside the
+        # gate/up GEMM of the next chunk on disjoint SMs (its rows feed NVLink meanwhile);
+        # only the common span is meaningful: swiglu = up to the end of gate/up, down =
+        # what is left of the down projection
         both = record("grouped_gemm_fp8_kernel: gate/up and down GEMMs overlapped "
                       f"({148 - down_sms} + {down_sms} SMs while both run)",
                       6.0 * rows * H * I, st["swiglu"] + st["down"],

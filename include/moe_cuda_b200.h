@@ -517,13 +517,12 @@ int moeb_ep_read_timing(moeb_ep_ctx *ctx, float *stage_ms6, int *steps);
 
 /* How moeb_ep_moe_forward (fused = 0) runs the two expert GEMMs on this context:
  * 0 = one after the other; 1 = in row chunks, the down projection of a chunk (whose rows
- * go home over NVLink) on a part of the SMs beside the gate/up GEMM of the next chunk;
- * 2 = two whole kernels side by side, the down kernel following row block by row block.
- * All three give the same bits. Chosen when the context is made: 0 unless the
- * environment variable MOEB_EP_MLP (seq | chunks | beside) says otherwise (measured at
- * 4 ranks the overlapped forms win nothing over 0);
- * MOEB_EP_MLP_CHUNKS (2..8, default 4) and MOEB_EP_DOWN_SMS (default 52) size modes 1, 2.
- * With modes 1 and 2 the stage times read "gate/up GEMM" up to the end of the last
+ * go home over NVLink) on a part of the SMs beside the gate/up GEMM of the next chunk
+ * (launches ordered by events on two streams; no kernel waits on another). Both give the
+ * same bits. Chosen when the context is made: 0 unless the environment variable
+ * MOEB_EP_MLP (seq | chunks) says otherwise (measured at 4 ranks the chunked form wins
+ * nothing); MOEB_EP_MLP_CHUNKS (2..8, default 4) and MOEB_EP_DOWN_SMS (default 52) size
+ * mode 1. With mode 1 the stage times read "gate/up GEMM" up to the end of the last
  * gate/up launch and "down GEMM" for what is left of the down projection after it.
  * Returns the mode, or -1 without a context. */
 int moeb_ep_mlp_mode(const moeb_ep_ctx *ctx);

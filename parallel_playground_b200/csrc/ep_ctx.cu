@@ -193,9 +193,9 @@ struct moeb_ep_ctx {
   // second stream and events for the overlapped MLP (host-side objects)
   cudaStream_t aux;
   cudaEvent_t ev_fork, ev_join, ev_chunk[8];
-  int mlp_mode;        // whole-layer call: 0 = GEMMs one after the other, 1 = in row chunks, 2 = side by side
+  int mlp_mode;        // whole-layer call: 0 = GEMMs one after the other, 1 = in row chunks
   int mlp_chunks;      // row chunks of mode 1
-  int down_ctas;       // SMs of the down kernel while a gate/up kernel runs beside it (modes 1 and 2)
+  int down_ctas;       // SMs of a chunk's down launch while the next chunk's gate/up launch runs
   // optional stage timing (host-side events, no device memory)
   bool timing;
   int timing_n;
@@ -345,7 +345,7 @@ ep_exchange_plan_kernel(const uint64_t* __restrict__ peer_base, size_t flags_off
     if (lane == 0) {
       arrive_need[b] = c;
       arrived[b] = 0;
-      inter_done[b] = 0;   // gate/up tiles finished per block (overlapped MLP)
+      inter_done[b] = 0;   // (scratch words of the chunked MLP)
     }
   }
 }
@@ -722,23 +722,19 @@ extern "C" int moeb_ep_create(const moeb_ep_config* cfg, const uint64_t* peer_ba
   set_output(c, nullptr, nullptr, 0);
   c->aux = nullptr;
   c->ev_fork = c->ev_join = nullptr;
-  // How the whole-layer call runs the two expert GEMMs (MOEB_EP_MLP = seq | chunks |
-  // beside). With more than one rank the down projection is bound by NVLink (most of
-  // its rows go to other ranks) and the link idles during gate/up. "chunks" splits the
-  // rows into MOEB_EP_MLP_CHUNKS ranges and runs the down projection of a range, on
-  // MOEB_EP_DOWN_SMS SMs, beside the gate/up GEMM of the next one. "beside" runs two
-  // whole kernels side by side, the down kernel waiting per row block for the gate/up
-  // kernel. Measured at 4 ranks (both GEMMs, ms): default workload seq 1.59, chunks
-  // 1.53 (4 ranges, 52 SMs; 6 ranges 1.59, 44 SMs 1.70), beside 1.62; DeepSeek-V3
-  // shape seq 1.86, chunks 1.89. What the overlap wins (the SM time the down kernel
-  // spends waiting for the link, at most 0.2 ms) goes into eight launches' ramps and
-  // tails (chunks) or into the store warp the gate/up kernel then carries (beside), so
-  // the default stays "seq" and the other two are options.
+  // How the whole-layer call runs the two expert GEMMs (MOEB_EP_MLP = seq | chunks).
+  // With more than one rank the down projection is bound by NVLink (most of its rows
+  // go to other ranks) and the link idles during gate/up. "chunks" splits the rows into
+  // MOEB_EP_MLP_CHUNKS ranges and runs the down projection of a range, on
+  // MOEB_EP_DOWN_SMS SMs, beside the gate/up GEMM of the next one. Measured at 4 ranks
+  // (both GEMMs, ms): default workload seq 1.59, chunks 1.53 (4 ranges, 52 SMs; 6 ranges
+  // 1.59, 44 SMs 1.70); DeepSeek-V3 shape seq 1.86, chunks 1.89. What the overlap wins
+  // (the SM time the down kernel spends waiting for the link, at most 0.2 ms) goes into
+  // eight launches' ramps and tails, so the default stays "seq".
   c->mlp_mode = 0;
   if (const char* o = getenv("MOEB_EP_MLP")) {
     if (!strcmp(o, "seq") || !strcmp(o, "0")) c->mlp_mode = 0;
     else if (!strcmp(o, "chunks")) c->mlp_mode = 1;
-    else if (!strcmp(o, "beside")) c->mlp_mode = 2;
   }
   c->mlp_chunks = 4;
   if (const char* o = getenv("MOEB_EP_MLP_CHUNKS")) c->mlp_chunks = atoi(o);
@@ -1014,10 +1010,8 @@ extern "C" int moeb_ep_moe_forward(moeb_ep_ctx* c, const moeb_layer_config* cfg,
   // status words: [0,4) gate/up GEMM and the rows it waits for, [4,8) down GEMM,
   // [8,12) rank barrier of the combine
   if (!fused && c->mlp_mode != 0) {
-    // dispatch, then the two GEMMs overlapped: in row chunks (the down projection of a
-    // chunk beside the gate/up GEMM of the next one), or as two whole kernels side by
-    // side with the down kernel following row block by row block; either way the down
-    // kernel's rows go home over NVLink while gate/up is still computing
+    // dispatch, then the two GEMMs in row chunks: the down projection of a chunk, whose
+    // rows go home over NVLink, beside the gate/up GEMM of the next one
     uint8_t* L = c->local;
     if ((rc = set_output(c, nullptr, nullptr, 0))) return rc;
     if ((rc = dispatch_send(c, x_bf16, nullptr, nullptr, indices, T, c->transport != 1, status_dev,
@@ -1027,26 +1021,15 @@ extern "C" int moeb_ep_moe_forward(moeb_ep_ctx* c, const moeb_layer_config* cfg,
     if ((rc = dispatch_recv(c, status_dev, s))) return rc;
     record_stage(c, 3, s);
     cudaEvent_t mid = (c->timing && c->timing_n < kTimingSlots) ? c->ev[c->timing_n][4] : nullptr;
-    if (c->mlp_mode == 1) {
-      // (the row-block counters of the side-by-side form hold the chunk plan here)
-      rc = fp8_mlp_chunked(c->out_x, c->out_scale, gate_q, gate_scale, up_q, up_scale, inter,
-                           inter_scale, down_q, down_scale, at<const uint64_t>(L, c->loc.peer_tab),
-                           c->sym.home, at<const int32_t>(L, c->loc.source_rank), c->pos32_cur,
-                           c->out_rows, at<const int32_t>(L, c->loc.m_valid), cfg->I, H, c->e_local,
-                           at<const int32_t>(L, c->loc.grouped_layout),
-                           at<int32_t>(L, c->loc.inter_done), c->mlp_chunks, c->down_ctas,
-                           status_dev, status_dev ? status_dev + 4 : nullptr, s, c->aux,
-                           c->ev_fork, c->ev_join, c->ev_chunk, mid);
-    } else {
-      rc = fp8_mlp_overlapped(
-          c->out_x, c->out_scale, gate_q, gate_scale, up_q, up_scale, inter, inter_scale, down_q,
-          down_scale, at<const uint64_t>(L, c->loc.peer_tab), c->sym.home,
-          at<const int32_t>(L, c->loc.source_rank), c->pos32_cur, c->out_rows,
-          at<const int32_t>(L, c->loc.m_valid), cfg->I, H, c->e_local,
-          at<const int32_t>(L, c->loc.grouped_layout), at<int32_t>(L, c->loc.inter_done),
-          c->down_ctas, status_dev, status_dev ? status_dev + 4 : nullptr, s, c->aux, c->ev_fork,
-          c->ev_join, mid);
-    }
+    // (the chunk plan lives in the per-block counter array, unused on this path)
+    rc = fp8_mlp_chunked(c->out_x, c->out_scale, gate_q, gate_scale, up_q, up_scale, inter,
+                         inter_scale, down_q, down_scale, at<const uint64_t>(L, c->loc.peer_tab),
+                         c->sym.home, at<const int32_t>(L, c->loc.source_rank), c->pos32_cur,
+                         c->out_rows, at<const int32_t>(L, c->loc.m_valid), cfg->I, H, c->e_local,
+                         at<const int32_t>(L, c->loc.grouped_layout),
+                         at<int32_t>(L, c->loc.inter_done), c->mlp_chunks, c->down_ctas, status_dev,
+                         status_dev ? status_dev + 4 : nullptr, s, c->aux, c->ev_fork, c->ev_join,
+                         c->ev_chunk, mid);
     if (rc) return rc;
     record_stage(c, 5, s);
     if ((rc = combine_recv(c, weights, out_bf16, 0, status_dev ? status_dev + 8 : nullptr, s)))

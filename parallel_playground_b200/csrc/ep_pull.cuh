@@ -62,16 +62,6 @@ int fp8_gemm_nt_scatter_off(const void* A, const float* scale_a, const void* W,
                             const int32_t* m_valid_dev, int N, int K, int G,
                             const int32_t* grouped_layout, int32_t* status_dev,
                             cudaStream_t stream);
-// grouped_gemm.cu: gate/up and down GEMM of a rank side by side on disjoint SMs.
-int fp8_mlp_overlapped(const void* A, const float* scale_a, const void* gate,
-                       const float* scale_gate, const void* up, const float* scale_up, void* D,
-                       float* scale_d, const void* down, const float* scale_down,
-                       const uint64_t* peer_out, size_t home_off, const int32_t* row_rank,
-                       const int32_t* row_pos, int m_total, const int32_t* m_valid_dev, int I,
-                       int H, int G, const int32_t* grouped_layout, int32_t* inter_done,
-                       int n_down_ctas, int32_t* status_swiglu, int32_t* status_down,
-                       cudaStream_t main, cudaStream_t aux, cudaEvent_t ev_fork,
-                       cudaEvent_t ev_join, cudaEvent_t ev_gate_up_done);
 // grouped_gemm.cu: the MLP in row chunks, gate/up of a chunk beside the down projection
 // of the chunk before it.
 int fp8_mlp_chunked(const void* A, const float* scale_a, const void* gate, const float* scale_gate,

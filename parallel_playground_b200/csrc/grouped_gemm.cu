@@ -110,12 +110,7 @@ struct GemmParams {
   const int32_t* arrive_need;  // [num_m_blocks] rows the block holds
   int n_comm;
   PullParams pull;
-  // Overlapped MLP (expert parallel): the gate/up kernel counts its finished tiles
-  // per row block (publish_cnt), the down kernel, running beside it on other SMs,
-  // waits until a row block has all its arrive_need_const tiles before it reads the
-  // block (arrive_cnt = that array, arrive_need = nullptr). max_ctas > 0 bounds the grid.
-  int32_t* publish_cnt;
-  int arrive_need_const;
+  // max_ctas > 0 bounds the grid (chunked MLP: a gate/up and a down launch share the SMs).
   int max_ctas;
   // Chunked MLP: optional device word, first row of this launch's range (a multiple of
   // 128 * group_m); the range ends at *m_valid. Row blocks before it are not visited.
@@ -301,14 +296,12 @@ __device__ __forceinline__ void fma_chunk(float2 (&acc)[64], const uint32_t (&v)
 // tanh.approx instead of ex2 + rcp (half the special-function work of the SwiGLU
 // epilogue).
 // kOptFused: dispatch fused into the GEMM (see GemmParams::arrive_cnt).
-// kOptPublish: the gate/up store warp counts finished tiles per row block for a
-// down kernel that runs at the same time (GemmParams::publish_cnt).
-constexpr int kOptOffload = 1, kOptEarly = 2, kOptTanh = 4, kOptFused = 8, kOptPublish = 16;
+constexpr int kOptOffload = 1, kOptEarly = 2, kOptTanh = 4, kOptFused = 8;
 // Fused dispatch: wait (bounded) until all rows of a 128-row block have been
 // published by the comm CTAs. Every lane of the warp polls the same word.
 __device__ __forceinline__ bool wait_rows_arrived(const GemmParams& p, int m_block,
                                                   volatile int* abort_flag) {
-  const int need = p.arrive_need != nullptr ? __ldg(p.arrive_need + m_block) : p.arrive_need_const;
+  const int need = __ldg(p.arrive_need + m_block);
   if (ld_acquire_gpu_s32(p.arrive_cnt + m_block) >= need) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
@@ -335,7 +328,6 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
   constexpr bool kEarly = (kOpt & kOptEarly) != 0;
   constexpr bool kTanh = (kOpt & kOptTanh) != 0;
   constexpr bool kFused = (kOpt & kOptFused) != 0;
-  constexpr bool kPublish = (kOpt & kOptPublish) != 0;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -536,14 +528,6 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a,
         __syncwarp();
         if (lane == 0) mbar_arrive(stage_free_bar(h));
         sphase ^= 1u;
-        if constexpr (kPublish) {
-          // the tile (rows by the copies above, scales by the promotion warps before
-          // they signalled) is in global memory: count it for the down kernel
-          bulk_wait_group0();
-          __threadfence();
-          __syncwarp();
-          if (lane == 0) red_release_gpu_add(p.publish_cnt + ti.m_block, 1);
-        }
       }
       bulk_wait_group0();          // every row has reached global memory
     }
@@ -1298,9 +1282,6 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
       // dispatch fused into this launch: n_comm CTAs pull rows, the rest compute
       kernel = grouped_gemm_fp8_kernel<true, false, kOptTanh | kOptFused>;
       n_comm = p.n_comm;
-    } else if (p.publish_cnt != nullptr) {
-      // a down kernel runs beside this launch and waits for its row blocks
-      kernel = grouped_gemm_fp8_kernel<true, false, kOptTanh | kOptOffload | kOptPublish>;
     }
   } else {
     // bf16 output, local or to peers: rows are staged in shared memory and leave
@@ -1308,9 +1289,6 @@ static int launch_grouped_gemm(const void* A, const void* B0, const void* B1, Ge
     if (p.scatter_out != nullptr || !p.out_f32) {
       kernel = plain ? grouped_gemm_fp8_kernel<false, true, 0>
                      : grouped_gemm_fp8_kernel<false, true, kOptOffload | kOptEarly>;
-      // beside a gate/up kernel that is still producing its input: wait per row block
-      if (p.arrive_cnt != nullptr)
-        kernel = grouped_gemm_fp8_kernel<false, true, kOptOffload | kOptEarly | kOptFused>;
       smem_bytes = kGemmSmemBytesScatter;
     }
   }
@@ -1439,76 +1417,6 @@ int moeb::fp8_swiglu_fused_dispatch(const void* A, const float* scale_a, const v
   return launch_grouped_gemm<true>(A, gate, up, p, stream);
 }
 
-// Both expert GEMMs of a rank at the same time, on disjoint sets of SMs, for the
-// expert-parallel layer: the gate/up kernel (stream `main`) counts its finished
-// tiles per 128-row block; the down kernel (stream `aux`, n_down_ctas CTAs) waits for
-// a block's I/128 tiles before it reads the block and sends its rows home over
-// NVLink while gate/up is still computing later blocks, so that the link is busy
-// during the whole MLP instead of during the down projection only. `inter_done`
-// ([m_total/128] int32) must be zero. The caller has made `aux` wait for `main` up to
-// this point (ev_fork) and joins it afterwards (ev_join).
-int moeb::fp8_mlp_overlapped(const void* A, const float* scale_a, const void* gate,
-                             const float* scale_gate, const void* up, const float* scale_up,
-                             void* D, float* scale_d, const void* down, const float* scale_down,
-                             const uint64_t* peer_out, size_t home_off, const int32_t* row_rank,
-                             const int32_t* row_pos, int m_total, const int32_t* m_valid_dev,
-                             int I, int H, int G, const int32_t* grouped_layout,
-                             int32_t* inter_done, int n_down_ctas, int32_t* status_swiglu,
-                             int32_t* status_down, cudaStream_t main, cudaStream_t aux,
-                             cudaEvent_t ev_fork, cudaEvent_t ev_join, cudaEvent_t ev_gate_up_done) {
-  int rc = check_common("fp8_mlp_overlapped", A, scale_a, gate, scale_gate, D, m_total, I, H, G,
-                        MOEB_GEMM_M_GROUPED_CONTIGUOUS, grouped_layout, 0);
-  if (rc != kOk) return rc;
-  if (!up || !scale_up || !scale_d || !down || !scale_down || !peer_out || !row_rank || !row_pos ||
-      !inter_done || !m_valid_dev || n_down_ctas <= 0 || n_down_ctas >= sm_count() ||
-      !aligned16(up) || !aligned16(down)) {
-    set_last_error_msg("fp8_mlp_overlapped: bad argument");
-    return kInvalidArgument;
-  }
-  GemmParams g{};
-  g.scale_a = scale_a;
-  g.scale_b0 = scale_gate;
-  g.scale_b1 = scale_up;
-  g.out = D;
-  g.scale_d = scale_d;
-  g.layout = grouped_layout;
-  g.status = status_swiglu;
-  g.m_total = m_total;
-  g.N = I;
-  g.K = H;
-  g.G = G;
-  g.m_valid = m_valid_dev;
-  g.publish_cnt = inter_done;
-  g.max_ctas = sm_count() - n_down_ctas;
-  GemmParams d{};
-  d.scale_a = scale_d;
-  d.scale_b0 = scale_down;
-  d.scale_b1 = scale_down;
-  d.layout = grouped_layout;
-  d.status = status_down;
-  d.m_total = m_total;
-  d.N = H;
-  d.K = I;
-  d.G = G;
-  d.m_valid = m_valid_dev;
-  d.scatter_out = peer_out;
-  d.scatter_off = home_off;
-  d.scatter_rank = row_rank;
-  d.scatter_pos = row_pos;
-  d.arrive_cnt = inter_done;
-  d.arrive_need = nullptr;
-  d.arrive_need_const = I / 128;
-  d.max_ctas = n_down_ctas;
-  MOEB_CUDA_TRY(cudaEventRecord(ev_fork, main));
-  MOEB_CUDA_TRY(cudaStreamWaitEvent(aux, ev_fork, 0));
-  if ((rc = launch_grouped_gemm<true>(A, gate, up, g, main)) != kOk) return rc;
-  if (ev_gate_up_done != nullptr) MOEB_CUDA_TRY(cudaEventRecord(ev_gate_up_done, main));
-  if ((rc = launch_grouped_gemm<false>(D, down, down, d, aux)) != kOk) return rc;
-  MOEB_CUDA_TRY(cudaEventRecord(ev_join, aux));
-  MOEB_CUDA_TRY(cudaStreamWaitEvent(main, ev_join, 0));
-  return kOk;
-}
-
 // Row ranges of a chunked MLP: plan[2c] = first row, plan[2c+1] = end row of chunk c.
 // The rows in use are split evenly into `chunks` ranges of whole groups of row blocks.
 __global__ void mlp_chunk_plan_kernel(const int32_t* __restrict__ m_valid, int chunks,
@@ -1530,9 +1438,9 @@ __global__ void mlp_chunk_plan_kernel(const int32_t* __restrict__ m_valid, int c
 // c (stream `aux`, n_down_ctas SMs), whose store warps send the rows home over NVLink.
 // The link, which bounds the down projection when most rows are remote, is then busy
 // from the end of the first gate/up chunk on instead of after the whole gate/up GEMM.
-// Unlike fp8_mlp_overlapped the kernels do not wait on one another: a chunk's down
-// launch follows its gate/up launch through an event, and both kernels keep the code
-// of the plain launches. The first gate/up chunk and the last down chunk have the GPU
+// No kernel waits on another: a chunk's down launch follows its gate/up launch through
+// an event, and both kernels are the plain launches' (two launches that poll one
+// another's progress must not share a GPU: nothing guarantees that both are resident). The first gate/up chunk and the last down chunk have the GPU
 // to themselves. `plan` holds 2 * chunks int32 (written here); ev_chunk: one event per
 // chunk. The result is that of the two plain launches, bit for bit.
 int moeb::fp8_mlp_chunked(const void* A, const float* scale_a, const void* gate,

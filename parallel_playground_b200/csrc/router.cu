@@ -15,9 +15,10 @@ namespace moeb {
 // ------------------------------------------------------------------ logits --
 // logits[T,E] = x[T,H] * W[H,E] (+ bias). <= 0.2 % of the layer's FLOPs, so it
 // must only not get in the way: the kernel streams x once from HBM (its bound)
-// and takes the small weight matrix from L2. bf16 mma.sync tiles (m16n8k16, fp32
-// accumulate) are plenty for a GEMM this thin; the tcgen05 path is reserved for
-// the expert GEMMs.
+// and takes the small weight matrix from L2. Up to 64 experts bf16 mma.sync tiles
+// (m16n8k16, fp32 accumulate) keep up with the stream; beyond that the contraction
+// itself becomes the limit of the mma.sync path and the logits go through the
+// tcgen05 bf16 GEMM when the caller brings a workspace (further down).
 //
 // CTA = 8 warps = TM token tiles (16 tokens each) x KS slices of the K range;
 // the slices are summed in slice order at the end (deterministic).

@@ -866,10 +866,10 @@ class EPContext:
     @property
     def mlp_mode(self) -> str:
         """How moe_forward(fused=False) runs the two expert GEMMs: "seq" (one after the
-        other), "chunks" (row chunks, down projection of a chunk beside the gate/up GEMM
-        of the next) or "beside" (two whole kernels side by side)."""
+        other) or "chunks" (row chunks, down projection of a chunk beside the gate/up
+        GEMM of the next)."""
         lib = cabi.load()
-        return ("seq", "chunks", "beside")[int(lib.moeb_ep_mlp_mode(self._ctx))]
+        return ("seq", "chunks")[int(lib.moeb_ep_mlp_mode(self._ctx))]
 
     def set_timing(self, on=True):
         cabi.call("moeb_ep_set_timing", self._ctx, int(bool(on)))

@@ -71,13 +71,11 @@ def _worker(rank, world, port, q):
         layer = lambda out, fused, x=d.x: ctx.moe_forward(  # noqa: E731
             x, d.w_router, None, d.gate, d.gate_scale, d.up, d.up_scale, d.down, d.down_scale, out,
             shape, fused=fused)
-        # the other ways to run the two expert GEMMs of the whole-layer call: one after the
-        # other, in row chunks (the down projection of a chunk beside the gate/up GEMM of
-        # the next), as two whole kernels side by side. Same bits every time.
+        # the other way to run the two expert GEMMs of the whole-layer call: in row chunks
+        # (the down projection of a chunk beside the gate/up GEMM of the next). Same bits.
         assert ctx.mlp_mode == "seq"
-        for mode, extra in (("seq", {}), ("chunks", {"MOEB_EP_MLP_CHUNKS": "3"}),
-                            ("chunks", {"MOEB_EP_MLP_CHUNKS": "8", "MOEB_EP_DOWN_SMS": "30"}),
-                            ("beside", {"MOEB_EP_DOWN_SMS": "40"})):
+        for mode, extra in (("chunks", {}), ("chunks", {"MOEB_EP_MLP_CHUNKS": "3"}),
+                            ("chunks", {"MOEB_EP_MLP_CHUNKS": "8", "MOEB_EP_DOWN_SMS": "30"})):
             os.environ.update(MOEB_EP_MLP=mode, **extra)
             other_mlp = EPContext(T, shape.E, k, H, device=rank)
             for key in ("MOEB_EP_MLP", *extra):

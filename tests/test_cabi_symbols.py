@@ -97,3 +97,23 @@ def test_compiled_extension_exposes_reference_names(lib):
     assert ext.all2all_symmetric_bytes(256, 8, 2, 128, 1024, 1) > 0
     assert int(ext.GemmType.MGroupedContiguous) == 1 and int(ext.GemmType.MGroupedMasked) == 2
     ext.init("", "")
+
+
+def test_router_workspace_query_is_host_only_and_monotone(lib):
+    """moeb_router_logits_workspace_bytes: 0 where the tensor-core path does not apply (few
+    tokens, up to 64 experts, E % 8 != 0, bad sizes); otherwise a size that also serves
+    every smaller token count, so one workspace sized for the most tokens is enough."""
+    q = lib.moeb_router_logits_workspace_bytes
+    assert q(8192, 4096, 32) == 0 and q(8192, 4096, 64) == 0      # narrow routers
+    assert q(512, 4096, 256) == 0                                  # few tokens
+    assert q(8192, 4096, 100) == 0                                 # E % 8 != 0
+    assert q(8192, 4100, 256) == 0 and q(0, 4096, 256) == 0 and q(8192, 4096, 0) == 0
+    big = q(8192, 4096, 256)
+    assert big >= 256 * 4096 * 2 + 8192 * 256 * 4
+    sizes = [q(t, 4096, 256) for t in (1024, 2048, 4096, 8192, 20000, 65536)]
+    assert all(b >= a > 0 for a, b in zip(sizes, sizes[1:]))
+    assert sizes[3] == big
+
+
+def test_ep_mode_query_without_a_context(lib):
+    assert lib.moeb_ep_mlp_mode(None) == -1

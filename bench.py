@@ -919,7 +919,7 @@ def measure_e2e(mc, layer, shape, inp, dev, world, args):
                      d.up, d.up_scale, d.down, d.down_scale, shape.router_mode, shape.n_group,
                      shape.topk_group, shape.renorm, shape.route_scale,
                      None if bias is None else bias.to(dev))
-    n = max(4, min(args.steps, 20))
+    n = e2e_batches(args)
     # two pinned host batches in, two out (alternating): consecutive steps use
     # different host buffers, as a caller feeding a stream of batches would
     xs = [inp.x.pin_memory(), inp.x.clone().pin_memory()]
@@ -967,6 +967,13 @@ def measure_e2e(mc, layer, shape, inp, dev, world, args):
                    "moeb_moe_forward_host call per batch"}
 
 
+def e2e_batches(args):
+    """Host batches of the end-to-end stream: twice the timed steps (at least 8, at most
+    60), so that filling and draining the three-stage pipeline (one copy-in before the
+    first layer call, one copy-out after the last) weighs a few per cent, not ten."""
+    return max(8, min(2 * args.steps, 60))
+
+
 def copy_only_ms(x_shape, dev, x_seq, o_seq):
     """ms per batch of the host pipeline with the layer replaced by a device-to-device
     copy: the ceiling the H2D + D2H copies alone allow."""
@@ -987,7 +994,7 @@ def measure_e2e_ep(mc, layer, shape, inp, dev, args):
     layer through the public ep.ep_moe_forward call and reads its result back."""
     import torch.distributed as dist
     from parallel_playground_b200.hostpipe import HostPipeline
-    n = max(4, min(args.steps, 20))
+    n = e2e_batches(args)
     xs = [inp.x.pin_memory(), inp.x.clone().pin_memory()]
     ohs = [torch.empty_like(inp.x).pin_memory() for _ in range(2)]
     x_seq = [xs[i & 1] for i in range(n)]

@@ -637,7 +637,7 @@ def parity_leg(mc, args, shape, inp, d, bias_d, dev, rank, world, layer):
         <= 1e-3;
       * the whole output equals, bit for bit, the output of the staged transport
         (pack -> NCCL all-to-all-v -> unpack), an independent second path.
-    The verdict is all-reduced; the oracle is the checker here, never the timed path."""
+    The outcome is all-reduced; the oracle is the checker here, never the timed path."""
     import numpy as np
     import torch.distributed as dist
     import oracle

@@ -68,6 +68,9 @@ def parse_args():
                     help="ctx transport: senders store each token once per destination rank and "
                          "the owners fan it out (push; auto picks it unless --ep-fused 1), or the "
                          "owners load every copy (pull)")
+    ap.add_argument("--targets", default=None,
+                    help="comma-separated workloads for the short target runs instead of the "
+                         "list of this N (e.g. the 8-GPU list on fewer GPUs)")
     ap.add_argument("--no-targets", action="store_true",
                     help="skip the short runs of the other configurations (the `targets` key)")
     ap.add_argument("--no-parity", action="store_true",
@@ -808,7 +811,8 @@ def run_b200(args):
         gc.collect()
         torch.cuda.empty_cache()
         targets = [run_target(mc, args, name, world, rank, local_rank, dev, peaks, fp8)
-                   for name in TARGET_WORKLOADS.get(world, [])]
+                   for name in (args.targets.split(",") if args.targets
+                                else TARGET_WORKLOADS.get(world, []))]
 
     if rank != 0:
         if world > 1:

@@ -236,6 +236,31 @@ def _worker(rank, world, port, q):
         kept = ~dropped
         assert torch.equal(bits(out6)[kept], bits(out_ref)[kept])
         small.close()
+
+        # one expert per rank (the Mixtral-shaped configuration at EP=8 has this form):
+        # wide experts, top-2, skewed load from a router bias; all forms against the staged one
+        sh1 = dataclasses.replace(wl.CONFIGS["mixtral"], T=192, H=512, I=1024, E=world,
+                                  k=min(2, world))
+        in1 = wl.make_layer_inputs(sh1, rank=rank, world=world)
+        d1 = in1.to(dev)
+        b1 = None if in1.router_bias is None else in1.router_bias.to(dev)
+        st1 = All2AllStaged(sh1.T, sh1.E, sh1.k, 128, sh1.H, in_dtype=torch.float8_e4m3fn,
+                            out_dtype=torch.bfloat16, device=rank)
+        ref1 = torch.empty((sh1.T, sh1.H), dtype=torch.bfloat16, device=dev)
+        ep_moe_forward(st1, d1.x, d1.w_router, b1, d1.gate, d1.gate_scale, d1.up, d1.up_scale,
+                       d1.down, d1.down_scale, ref1, sh1)
+        torch.cuda.synchronize()
+        one = EPContext(sh1.T, sh1.E, sh1.k, sh1.H, device=rank)
+        for fused in (False, True, False):
+            o1 = torch.full_like(ref1, 2.0)
+            one.moe_forward(d1.x, d1.w_router, b1, d1.gate, d1.gate_scale, d1.up, d1.up_scale,
+                            d1.down, d1.down_scale, o1, sh1, fused=fused)
+            torch.cuda.synchronize()
+            mc.check_device_status()
+            assert int(one.overflow.item()) == 0
+            assert torch.equal(bits(o1), bits(ref1)), ("one expert per rank", fused)
+        assert torch.equal(one.tokens_per_expert, st1._tokens_per_expert)
+        one.close()
         dist.barrier()
         pull_ctx.close()
         ctx.close()

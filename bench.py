@@ -458,7 +458,7 @@ def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused, mode="auto"
         hit[:, rank] = False
         return int(hit.sum().item())
 
-    # router x2, plan x3, exchange+plan, then push: dispatch, barrier, fan-out;
+    # router x2, plan x3, exchange+plan, then push: dispatch, barrier, fan-out, transpose;
     # pull: cast, mark, announce, pull (or inside the GEMM), pos; gate/up GEMM, down GEMM,
     # barrier, reduce
     # how the library runs the two expert GEMMs of the whole-layer call: one after the
@@ -470,7 +470,7 @@ def build_ep_step_ctx(mc, shape, d, bias_d, dev, rank, world, fused, mode="auto"
     # chunked: one plan kernel and two GEMM launches per chunk instead of two launches
     extra = 2 * chunks - 1 if mlp_mode == "chunks" else 0
     extra += router_extra_launches(mc, shape, bias_d is not None)
-    layer = {"kernels_per_step": (13 if push else (15 if fused else 16)) + extra, "out": out,
+    layer = {"kernels_per_step": (14 if push else (15 if fused else 16)) + extra, "out": out,
              "ctx": ctx, "mlp_mode": mlp_mode, "mlp_chunks": chunks if mlp_mode == "chunks" else 0,
              "mlp_overlapped": overlapped, "down_sms": down_sms if overlapped else 0,
              "run": run, "routed_rows": lambda: int(ctx.tokens_per_expert.sum().item()),

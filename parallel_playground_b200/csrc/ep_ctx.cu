@@ -489,7 +489,7 @@ static int set_output(moeb_ep_ctx* c, void* out_x, float* out_scale, int out_row
   // (every rank's senders bound their rows by max_recv_rows, so the caller's
   // tensors must have exactly that many rows, as the reference's do)
   if (!out_x || !out_scale || out_rows != c->m_cap ||
-      ((reinterpret_cast<uintptr_t>(out_x) | reinterpret_cast<uintptr_t>(out_scale)) & 15u) != 0) {
+      (reinterpret_cast<uintptr_t>(out_x) & 15u) != 0) {
     set_last_error_msg(
         "moeb_ep_dispatch: out_expert_x [max_recv_rows, H] and out_expert_x_scale "
         "[H/128, max_recv_rows] come together, 16-byte aligned");
@@ -608,16 +608,19 @@ static int dispatch_recv(moeb_ep_ctx* c, int32_t* status, cudaStream_t s) {
   }
   if (c->push_cur) {
     // every rank's stores have landed (rank barrier), then the owner-side fan-out
-    // of the stash rows, scales straight into the MN-major layout the GEMM reads
+    // of the stash rows and the scales' way to MN-major
     uint8_t* L = c->local;
     int rc = fence(c, status, s);
     if (rc) return rc;
     const int32_t* m_valid = at<const int32_t>(L, c->loc.m_valid);
-    if ((rc = ep_unstash_mn(c->sym_mine + c->sym.stash_x,
-                            at<const float>(c->sym_mine, c->sym.stash_scale),
-                            at<const int32_t>(L, c->loc.source_rank), c->pos32_cur, m_valid,
-                            c->out_rows, c->cfg.top_k, c->cfg.max_tokens, c->cfg.hidden, c->out_x,
-                            c->out_scale, s)))
+    if ((rc = moeb_ep_unstash(c->sym_mine + c->sym.stash_x,
+                              at<const float>(c->sym_mine, c->sym.stash_scale),
+                              at<const int32_t>(L, c->loc.source_rank), c->pos32_cur, m_valid,
+                              c->out_rows, c->cfg.top_k, c->cfg.max_tokens, c->cfg.hidden, c->out_x,
+                              at<float>(L, c->loc.scale_stage), s)))
+      return rc;
+    if ((rc = moeb_ep_scale_transpose(at<const float>(L, c->loc.scale_stage), m_valid, c->out_rows,
+                                      c->cfg.hidden / 128, c->out_scale, s)))
       return rc;
     c->received = true;
     return kOk;

@@ -214,45 +214,6 @@ ep_unstash_kernel(const uint8_t* __restrict__ stash_x, const float* __restrict__
   }
 }
 
-// The same fan-out with the scales written MN-major [n_kb, m_cap] at once (what the GEMM
-// reads), so that no transpose pass follows. One warp per 8 consecutive rows: the rows'
-// bytes are copied one after the other; lane kb then holds the 8 rows' scales of K block
-// kb and stores them as one 32-byte run. Rows without a source (padding) get scale 1.
-__global__ void __launch_bounds__(256)
-ep_unstash_mn_kernel(const uint8_t* __restrict__ stash_x, const float* __restrict__ stash_scale,
-                     const int32_t* __restrict__ source_rank, const int32_t* __restrict__ pos,
-                     const int32_t* __restrict__ m_valid, int m_cap, int k, int t_max, int H,
-                     uint8_t* __restrict__ x_out, float* __restrict__ scale_mn) {
-  const int rows = min(*m_valid, m_cap);     // a multiple of 128
-  const int n_kb = H / kQuantBlock;
-  const int lane = threadIdx.x & 31;
-  const int warps = (gridDim.x * blockDim.x) >> 5;
-  for (int r0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 8; r0 < rows; r0 += warps * 8) {
-    long long srow[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int src = source_rank[r0 + j];
-      srow[j] = src < 0 ? -1 : (long long)src * t_max + pos[r0 + j] / k;
-    }
-#pragma unroll 2
-    for (int j = 0; j < 8; ++j) {
-      if (srow[j] < 0) continue;
-      const uint4* from = reinterpret_cast<const uint4*>(stash_x + (size_t)srow[j] * H);
-      uint4* to = reinterpret_cast<uint4*>(x_out + (size_t)(r0 + j) * H);
-      for (int i = lane; i < H / 16; i += 32) to[i] = from[i];
-    }
-    for (int kb = lane; kb < n_kb; kb += 32) {
-      float v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        v[j] = srow[j] < 0 ? 1.0f : stash_scale[(size_t)srow[j] * n_kb + kb];
-      float4* o = reinterpret_cast<float4*>(scale_mn + (size_t)kb * m_cap + r0);
-      o[0] = make_float4(v[0], v[1], v[2], v[3]);
-      o[1] = make_float4(v[4], v[5], v[6], v[7]);
-    }
-  }
-}
-
 // Owner side: scale staging [rows, n_kb] (row-major, as received) -> [n_kb, m_cap]
 // (MN-major, what the GEMM reads). Only rows < *m_valid are touched.
 __global__ void __launch_bounds__(256)
@@ -493,26 +454,6 @@ extern "C" int moeb_ep_unstash(const void* stash_x, const float* stash_scale,
   ep_unstash_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
       (const uint8_t*)stash_x, stash_scale, source_rank, pos, m_valid, m_cap, k, t_max, H,
       (uint8_t*)expert_x, scale_staging);
-  MOEB_CUDA_TRY(cudaGetLastError());
-  return kOk;
-}
-
-// Fan-out of the stash rows with MN-major scales in one launch (the expert-parallel
-// context's receive half; m_cap must be a multiple of 8 and scale_mn 16-byte aligned).
-int moeb::ep_unstash_mn(const void* stash_x, const float* stash_scale, const int32_t* source_rank,
-                        const int32_t* pos, const int32_t* m_valid, int m_cap, int k, int t_max,
-                        int H, void* expert_x, float* scale_mn, cudaStream_t stream) {
-  if (!stash_x || !stash_scale || !source_rank || !pos || !m_valid || !expert_x || !scale_mn ||
-      m_cap <= 0 || m_cap % 8 != 0 || k <= 0 || t_max <= 0 || H <= 0 || H % kQuantBlock != 0 ||
-      (reinterpret_cast<uintptr_t>(scale_mn) & 15u) != 0) {
-    set_last_error_msg("ep_unstash_mn: bad argument");
-    return kInvalidArgument;
-  }
-  const int groups = ceil_div(m_cap, 8);
-  const int blocks = ceil_div(groups, 8) < 148 * 8 ? ceil_div(groups, 8) : 148 * 8;
-  ep_unstash_mn_kernel<<<blocks, 256, 0, stream>>>(
-      (const uint8_t*)stash_x, stash_scale, source_rank, pos, m_valid, m_cap, k, t_max, H,
-      (uint8_t*)expert_x, scale_mn);
   MOEB_CUDA_TRY(cudaGetLastError());
   return kOk;
 }

@@ -72,10 +72,6 @@ int fp8_mlp_chunked(const void* A, const float* scale_a, const void* gate, const
                     int32_t* plan, int chunks, int n_down_ctas, int32_t* status_swiglu,
                     int32_t* status_down, cudaStream_t main, cudaStream_t aux, cudaEvent_t ev_fork,
                     cudaEvent_t ev_join, const cudaEvent_t* ev_chunk, cudaEvent_t ev_gate_up_done);
-// ep_p2p.cu: owner-side fan-out of the stash rows, scales written MN-major at once.
-int ep_unstash_mn(const void* stash_x, const float* stash_scale, const int32_t* source_rank,
-                  const int32_t* pos, const int32_t* m_valid, int m_cap, int k, int t_max, int H,
-                  void* expert_x, float* scale_mn, cudaStream_t stream);
 // ep_p2p.cu: moeb_ep_dispatch_once that also fills the home-row map (-1: dropped).
 int ep_dispatch_once_home(const void* x_bf16, const int32_t* indices, const int32_t* send_row,
                           const int32_t* send_offsets, const int32_t* dest_base, int T, int t_max,
